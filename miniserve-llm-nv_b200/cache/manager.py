@@ -1,7 +1,7 @@
 """The cache manager: who holds which pages and state slots, as plain host-side bookkeeping.
 
 One :class:`PageAllocator` per *paged group* (layers whose mixers keep the same form of keys
-and values; a group with a sliding window is separate from one that keeps everything), one
+and values, or of latent vectors; a group with a sliding window is separate from one that keeps everything), one
 block table per request and group, one state slot per request.  A step is a transaction, as in
 miniserve/kv/manager.py:119-192: :meth:`prepare` reserves the pages the step's new tokens need
 and computes their slots, :meth:`commit` makes the new lengths and pages permanent (and gives
@@ -20,7 +20,7 @@ from dataclasses import dataclass, field
 import numpy
 from typing import Optional, Sequence
 
-from ..parts.base import PagedKVNeed, StateNeed
+from ..parts.base import PAGED_NEEDS, StateNeed
 from .allocator import OutOfPagesError, PageAllocator
 from .prefix import PrefixCache, PrefixEntry
 from .state_slots import StateSlots
@@ -91,13 +91,13 @@ class CacheManager:
             raise ValueError("page size must be at least 1")
         self.page_size = page_size
         self.num_pages = num_pages
-        self.paged_needs: list[PagedKVNeed] = [g.need for g in groups if isinstance(g.need, PagedKVNeed)]
+        self.paged_needs: list = [g.need for g in groups if isinstance(g.need, PAGED_NEEDS)]
         self.state_needs: list[StateNeed] = [g.need for g in groups if isinstance(g.need, StateNeed)]
         # position of every model group among the paged / state groups
         self.group_index: list[tuple[str, int]] = []
         paged = state = 0
         for g in groups:
-            if isinstance(g.need, PagedKVNeed):
+            if isinstance(g.need, PAGED_NEEDS):
                 self.group_index.append(("paged", paged))
                 paged += 1
             else:

@@ -2,7 +2,8 @@
 the sampling records of the state slots.
 
 A paged group's pools have the shape ``[runs, pages + 1, kv_heads, page_size, head_dim]`` for
-keys and the same for values (the layout of miniserve/kv/layout.py:65-75 per group); the last
+keys and the same for values (the layout of miniserve/kv/layout.py:65-75 per group); a group of
+latent vectors has one pool ``[runs, pages + 1, page_size, rank + rot]``; the last
 page is a scratch page that no request ever holds: padding rows of a replayed CUDA graph write
 to it.  State tensors and sampling records likewise have one slot more than there are requests,
 the scratch slot, which padding rows read and write.  Pools are allocated once and never move.
@@ -16,8 +17,8 @@ from typing import Sequence
 import torch
 
 from ..kernels import SAMPLING_RECORD_WORDS
-from ..parts.base import PagedKVNeed, StateNeed
-from ..parts.context import PagedKVView, StateView, StepContext
+from ..parts.base import PAGED_NEEDS, PagedKVNeed, PagedLatentNeed, StateNeed
+from ..parts.context import PagedKVView, PagedLatentView, StateView, StepContext
 from ..parts.model import CacheGroup, RunCache
 
 
@@ -38,6 +39,13 @@ class CacheStorage:
                 shape = (group.n_slots, num_pages + 1, need.num_kv_heads, page_size, need.head_dim)
                 self.key_pools.append(torch.zeros(shape, dtype=dtype, device=device))
                 self.value_pools.append(torch.zeros(shape, dtype=dtype, device=device))
+                self.states.append(None)
+                self.paged_index.append(paged)
+                paged += 1
+            elif isinstance(need, PagedLatentNeed):
+                shape = (group.n_slots, num_pages + 1, page_size, need.rank + need.rot)
+                self.key_pools.append(torch.zeros(shape, dtype=dtype, device=device))     # the group's only pool
+                self.value_pools.append(None)
                 self.states.append(None)
                 self.paged_index.append(paged)
                 paged += 1
@@ -62,10 +70,12 @@ class CacheStorage:
 
     @staticmethod
     def bytes_per_page(groups: Sequence[CacheGroup], page_size: int, dtype: torch.dtype) -> int:
-        """Bytes one page number costs across all paged groups (keys and values, all runs)."""
+        """Bytes one page number costs across all paged groups (keys and values or latent vectors, all runs)."""
         size = torch.empty((), dtype=dtype).element_size()
-        return sum(2 * g.n_slots * g.need.num_kv_heads * page_size * g.need.head_dim * size
-                   for g in groups if isinstance(g.need, PagedKVNeed))
+        return (sum(2 * g.n_slots * g.need.num_kv_heads * page_size * g.need.head_dim * size
+                    for g in groups if isinstance(g.need, PagedKVNeed))
+                + sum(g.n_slots * page_size * (g.need.rank + g.need.rot) * size
+                      for g in groups if isinstance(g.need, PagedLatentNeed)))
 
     def run_view(self, plan: RunCache, ctx: StepContext):
         """The cache of one layer run for this step."""
@@ -74,6 +84,9 @@ class CacheStorage:
             block_tables, slots = ctx.group_views[self.paged_index[plan.group]]
             return PagedKVView(self.key_pools[plan.group][plan.slot], self.value_pools[plan.group][plan.slot],
                                block_tables, slots, self.page_size, plan.writable)
+        if isinstance(need, PagedLatentNeed):
+            block_tables, slots = ctx.group_views[self.paged_index[plan.group]]
+            return PagedLatentView(self.key_pools[plan.group][plan.slot], block_tables, slots, self.page_size, plan.writable)
         return StateView(self.states[plan.group][plan.slot])
 
     def reset_slot(self, slot: int, temperature: float, top_p: float, top_k: int, seed: int) -> None:

@@ -134,3 +134,157 @@ class Qwen3Config:
             "sliding_window": None,
             "use_sliding_window": False,
         }
+
+
+# --------------------------------------------------------------------------- Vesidra
+
+
+def _section(data: Mapping[str, Any], key: str, where: str) -> Mapping[str, Any]:
+    value = data.get(key)
+    if not isinstance(value, Mapping):
+        raise ValueError(f"{where}{key} must be an object in the model config, got {value!r}")
+    return value
+
+
+def _positive(data: Mapping[str, Any], key: str, where: str) -> float:
+    value = _number(data, key)
+    if not math.isfinite(value) or value <= 0:
+        raise ValueError(f"{where}{key} must be finite and positive, got {value}")
+    return value
+
+
+@dataclass(frozen=True)
+class RotationConfig:
+    """A rotary position encoding: ``dims`` rotated entries with base ``base``; ``scaling`` is None or the YaRN
+    constants (factor, original context, fast and slow turn counts)."""
+
+    base: float
+    dims: int
+    scaling: Any = None      # None or a tuple (factor, original, fast, slow)
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], where: str) -> "RotationConfig":
+        scaling = data.get("scaling")
+        if scaling is not None:
+            scaling = _section(data, "scaling", where)
+            scaling = tuple(_positive(scaling, key, where + "scaling.") for key in ("factor", "original", "fast", "slow"))
+        config = cls(base=_positive(data, "base", where), dims=_integer(data, "dims"), scaling=scaling)
+        if config.dims % 2:
+            raise ValueError(f"{where}dims {config.dims} is odd; the rotation pairs entry i with entry i + dims/2")
+        if config.base == 1.0:
+            raise ValueError(f"{where}base must differ from 1")
+        return config
+
+    def scaling_dict(self):
+        return None if self.scaling is None else dict(zip(("factor", "original", "fast", "slow"), self.scaling))
+
+
+@dataclass(frozen=True)
+class LatentAttentionConfig:
+    heads: int
+    dim: int
+    rot_dim: int
+    vdim: int
+    kv_rank: int
+    scale: float
+    rot: RotationConfig
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], where: str) -> "LatentAttentionConfig":
+        config = cls(heads=_integer(data, "heads"), dim=_integer(data, "dim"), rot_dim=_integer(data, "rot_dim"),
+                     vdim=_integer(data, "vdim"), kv_rank=_integer(data, "kv_rank"), scale=_positive(data, "scale", where),
+                     rot=RotationConfig.from_dict(_section(data, "rot", where), where + "rot."))
+        if config.rot.dims > config.rot_dim:
+            raise ValueError(f"{where}rot.dims {config.rot.dims} exceeds the rotated part rot_dim {config.rot_dim}")
+        return config
+
+
+@dataclass(frozen=True)
+class VesidraFeedForwardConfig:
+    """``kind`` "dense": a gated feed-forward of inner size ``ff``.  ``kind`` "moe": ``experts`` experts of inner size
+    ``ff`` of which a token uses ``top``, and a shared expert of inner size ``shared_ff`` (None: no shared expert)."""
+
+    kind: str
+    ff: int
+    experts: int = 0
+    top: int = 0
+    shared_ff: Any = None
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], where: str) -> "VesidraFeedForwardConfig":
+        kind = data.get("kind")
+        if kind == "dense":
+            return cls(kind="dense", ff=_integer(data, "ff"))
+        if kind == "moe":
+            router = _section(data, "router", where)
+            shared = data.get("shared")
+            config = cls(kind="moe", ff=_integer(_section(data, "expert", where), "ff"), experts=_integer(router, "experts"),
+                         top=_integer(router, "top"), shared_ff=None if shared is None else _integer(_section(data, "shared", where), "ff"))
+            if config.top > config.experts:
+                raise ValueError(f"{where}router.top {config.top} exceeds router.experts {config.experts}")
+            return config
+        raise UnsupportedModelError(f"UNSUPPORTED_MODEL_CONFIGURATION: {where}kind {kind!r} is not implemented (dense, moe)")
+
+
+@dataclass(frozen=True)
+class VesidraLayerConfig:
+    type: str
+    mixer: LatentAttentionConfig
+    mlp: Any      # VesidraFeedForwardConfig or None
+
+
+@dataclass(frozen=True)
+class VesidraConfig:
+    """The Vesidra decoder: ``config.json`` holds ``architecture``, ``vocab``, ``width``, ``embedding.scale``,
+    ``norm.eps`` and ``layers``, a list whose entries give each layer's mixer ``type``, the mixer's sizes and
+    constants (``mixer``) and its feed-forward (``mlp``, or null).  Every size and constant is read; nothing is
+    inferred from another."""
+
+    vocab: int
+    width: int
+    embedding_scale: float
+    eps: float
+    layers: tuple
+    architecture: str = "Vesidra"
+
+    MIXERS = ("latent_attention",)
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any]) -> "VesidraConfig":
+        if data.get("architecture") != "Vesidra":
+            raise UnsupportedModelError(f"UNSUPPORTED_MODEL_CONFIGURATION: expected architecture 'Vesidra', got {data.get('architecture')!r}")
+        raw_layers = data.get("layers")
+        if not isinstance(raw_layers, (list, tuple)) or not raw_layers:
+            raise ValueError("layers must be a non-empty list in the model config")
+        layers = []
+        for index, raw in enumerate(raw_layers):
+            where = f"layers[{index}]."
+            if not isinstance(raw, Mapping):
+                raise ValueError(f"layers[{index}] must be an object")
+            kind = raw.get("type")
+            if kind not in cls.MIXERS:
+                raise UnsupportedModelError(f"UNSUPPORTED_MODEL_CONFIGURATION: {where}type {kind!r} is not implemented "
+                                            f"({', '.join(cls.MIXERS)})")
+            mixer = LatentAttentionConfig.from_dict(_section(raw, "mixer", where), where + "mixer.")
+            mlp = None if raw.get("mlp") is None else VesidraFeedForwardConfig.from_dict(_section(raw, "mlp", where), where + "mlp.")
+            layers.append(VesidraLayerConfig(kind, mixer, mlp))
+        return cls(vocab=_integer(data, "vocab"), width=_integer(data, "width"),
+                   embedding_scale=_positive(_section(data, "embedding", ""), "scale", "embedding."),
+                   eps=_positive(_section(data, "norm", ""), "eps", "norm."), layers=tuple(layers))
+
+    def to_dict(self) -> dict[str, Any]:
+        """The ``config.json`` content that reads back as this configuration."""
+        layers = []
+        for layer in self.layers:
+            m = layer.mixer
+            mixer = dict(heads=m.heads, dim=m.dim, rot_dim=m.rot_dim, vdim=m.vdim, kv_rank=m.kv_rank, scale=m.scale,
+                         rot=dict(base=m.rot.base, dims=m.rot.dims, scaling=m.rot.scaling_dict()))
+            mlp = None
+            if layer.mlp is not None and layer.mlp.kind == "dense":
+                mlp = dict(kind="dense", ff=layer.mlp.ff)
+            elif layer.mlp is not None:
+                mlp = dict(kind="moe", expert=dict(ff=layer.mlp.ff), router=dict(experts=layer.mlp.experts, top=layer.mlp.top),
+                           shared=None if layer.mlp.shared_ff is None else dict(ff=layer.mlp.shared_ff))
+            layers.append(dict(type=layer.type, mixer=mixer, mlp=mlp))
+        return dict(architecture=self.architecture, vocab=self.vocab, width=self.width,
+                    embedding=dict(scale=self.embedding_scale), norm=dict(eps=self.eps), layers=layers)

@@ -49,9 +49,12 @@ def _load_builtin() -> None:
 
 
 def resolve_architecture(config: Mapping[str, Any]) -> Architecture:
-    """The registered architecture that ``config['architectures']`` names (exactly one name)."""
+    """The registered architecture that ``config['architectures']`` names (exactly one name), or, in configurations
+    that spell it so, the string ``config['architecture']``."""
     _load_builtin()
     names = config.get("architectures") or ()
+    if not names and isinstance(config.get("architecture"), str):
+        names = [config["architecture"]]
     if not isinstance(names, (list, tuple)) or len(names) != 1 or not isinstance(names[0], str):
         raise UnsupportedModelError(
             f"UNSUPPORTED_MODEL_CONFIGURATION: config.json must name exactly one architecture, got {names!r}; "

@@ -33,12 +33,13 @@ __global__ void scale_softcap_kernel(float* __restrict__ x, size_t total, float 
 
 // ---------------------------------------------------------------- residual add + RMSNorm
 // For output row k (source row r = rows ? rows[k] : k):
-//   x = residual[r] + delta[r]            (float32; written back to residual unless gathered)
+//   x = residual[r] + (delta[r] + delta2[r])   (float32; written back to residual unless gathered)
 //   out[k] = weight * x * rsqrt(mean(x^2) + eps)   rounded once to T
-// `delta` may be null (no add).  The weight keeps its stored type (float32 or bfloat16).
+// `delta` may be null (no add); `delta2` (only beside `delta`) is a second output of the same layer, as a block whose
+// mixer and feed-forward read the same input produces them.  The weight keeps its stored type (float32 or bfloat16).
 template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
-                                   const void* __restrict__ weight, int weight_dtype,
+                                   const T* __restrict__ delta2, const void* __restrict__ weight, int weight_dtype,
                                    const int* __restrict__ rows, T* __restrict__ out,
                                    int hidden, float eps) {
   grid_dependency_wait();
@@ -48,11 +49,12 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
   const size_t r = rows ? (size_t)rows[k] : k;
   float* res = residual + r * hidden;
   const T* del = delta ? delta + r * hidden : nullptr;
+  const T* del2 = delta2 ? delta2 + r * hidden : nullptr;
   const bool write_back = (rows == nullptr) && (delta != nullptr);
   float sum_sq = 0.f;
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
     float x = res[c];
-    if (del) x += to_float(del[c]);
+    if (del) x += del2 ? to_float(del[c]) + to_float(del2[c]) : to_float(del[c]);
     if (write_back) res[c] = x;
     sum_sq += x * x;
   }
@@ -61,7 +63,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
   T* dst = out + k * hidden;
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
     float x = res[c];
-    if (del && !write_back) x += to_float(del[c]);
+    if (del && !write_back) x += del2 ? to_float(del[c]) + to_float(del2[c]) : to_float(del[c]);
     dst[c] = from_float<T>(load_as_float(weight, weight_dtype, c) * (x * inv));
   }
 }
@@ -87,9 +89,9 @@ __global__ void rmsnorm_kernel(const T* __restrict__ x, const void* __restrict__
 }
 
 // ---------------------------------------------------------------- rotation tables
-// cos_sin[n, j] = (cos, sin)(float(position[n]) * inv_freq[j]) for j < half, in float32.
+// cos_sin[n, j] = magnitude * (cos, sin)(float(position[n]) * inv_freq[j]) for j < half, in float32.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
-                                  float2* __restrict__ cos_sin, int n_tokens, int half) {
+                                  float2* __restrict__ cos_sin, int n_tokens, int half, float magnitude) {
   grid_dependency_wait();
   grid_dependency_launch();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -98,7 +100,7 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
   const float angle = (float)positions[n] * inv_freq[j];
   float s, c;
   sincosf(angle, &s, &c);
-  cos_sin[i] = make_float2(c, s);
+  cos_sin[i] = make_float2(magnitude * c, magnitude * s);
 }
 
 // ---------------------------------------------------------------- q/k norm + rotation + cache append
@@ -234,16 +236,17 @@ MS_EXPORT int ms_scale_softcap(float* x, long long total, float scale, float cap
   return 0;
 }
 
-MS_EXPORT int ms_add_rmsnorm(float* residual, const void* delta, int dtype, const void* weight, int weight_dtype,
+MS_EXPORT int ms_add_rmsnorm(float* residual, const void* delta, const void* delta2, int dtype, const void* weight, int weight_dtype,
                              const int* rows, void* out, int n_out, int hidden, float eps, cudaStream_t stream) {
   if (n_out == 0) return 0;
   MS_REQUIRE(hidden > 0, "add_rmsnorm: hidden size must be positive, got %d", hidden);
+  MS_REQUIRE(delta != nullptr || delta2 == nullptr, "add_rmsnorm: a second output to add needs a first");
   if (hidden % 8 == 0 && hidden <= 8192) {
     const int groups = hidden / 8;
     const int threads = groups >= 256 ? 256 : ((groups + 31) / 32) * 32;
     const int chunks = (groups + threads - 1) / threads;
 #define MS_ADD_RMSNORM_VEC(C)                                                                                     \
-  MS_DISPATCH(dtype, (ms::launch(add_rmsnorm_vec_kernel<T, C>, n_out, threads, 0, stream, residual, (const T*)delta, weight, \
+  MS_DISPATCH(dtype, (ms::launch(add_rmsnorm_vec_kernel<T, C>, n_out, threads, 0, stream, residual, (const T*)delta, (const T*)delta2, weight, \
                                                                                weight_dtype, rows, (T*)out, hidden, eps)))
     if (chunks == 1) { MS_ADD_RMSNORM_VEC(1); } else if (chunks == 2) { MS_ADD_RMSNORM_VEC(2); } else { MS_ADD_RMSNORM_VEC(4); }
 #undef MS_ADD_RMSNORM_VEC
@@ -251,7 +254,7 @@ MS_EXPORT int ms_add_rmsnorm(float* residual, const void* delta, int dtype, cons
     return 0;
   }
   const int threads = hidden >= 1024 ? 256 : 128;
-  MS_DISPATCH(dtype, (ms::launch(add_rmsnorm_kernel<T>, n_out, threads, 0, stream, residual, (const T*)delta, weight,
+  MS_DISPATCH(dtype, (ms::launch(add_rmsnorm_kernel<T>, n_out, threads, 0, stream, residual, (const T*)delta, (const T*)delta2, weight,
                                                                          weight_dtype, rows, (T*)out, hidden, eps)));
   MS_CHECK_LAUNCH("add_rmsnorm");
   return 0;
@@ -269,10 +272,10 @@ MS_EXPORT int ms_rmsnorm(const void* x, int dtype, const void* weight, int weigh
 }
 
 MS_EXPORT int ms_rope_table(const int* positions, const float* inv_freq, float* cos_sin, int n_tokens, int half,
-                            cudaStream_t stream) {
+                            float magnitude, cudaStream_t stream) {
   if (n_tokens == 0 || half == 0) return 0;
   const int total = n_tokens * half;
-  ms::launch(rope_table_kernel, (total + 255) / 256, 256, 0, stream, positions, inv_freq, (float2*)cos_sin, n_tokens, half);
+  ms::launch(rope_table_kernel, (total + 255) / 256, 256, 0, stream, positions, inv_freq, (float2*)cos_sin, n_tokens, half, magnitude);
   MS_CHECK_LAUNCH("rope_table");
   return 0;
 }

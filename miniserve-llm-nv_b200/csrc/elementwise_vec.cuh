@@ -87,7 +87,7 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, const Vec8& x, int offs
 // so the row is read once.  Requires hidden % 8 == 0 and hidden <= 8 * blockDim.x * CHUNKS.
 template <typename T, int CHUNKS>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
-                                       const void* __restrict__ weight, int weight_dtype,
+                                       const T* __restrict__ delta2, const void* __restrict__ weight, int weight_dtype,
                                        const int* __restrict__ rows, T* __restrict__ out, int hidden, float eps) {
   grid_dependency_wait();
   grid_dependency_launch();
@@ -96,6 +96,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __
   const size_t r = rows ? (size_t)rows[k] : k;
   float* res = residual + r * hidden;
   const T* del = delta ? delta + r * hidden : nullptr;
+  const T* del2 = delta2 ? delta2 + r * hidden : nullptr;      // (only with delta: the stream gets delta + delta2)
   const bool write_back = (rows == nullptr) && (delta != nullptr);
   Vec8 x[CHUNKS];
   float sum_sq = 0.f;
@@ -105,7 +106,12 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __
     if (c < hidden) {
       x[i] = load8(res + c);
       if (del) {
-        const Vec8 d = load8(del + c);
+        Vec8 d = load8(del + c);
+        if (del2) {
+          const Vec8 d2 = load8(del2 + c);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) d.v[e] += d2.v[e];
+        }
 #pragma unroll
         for (int e = 0; e < 8; ++e) x[i].v[e] += d.v[e];
         if (write_back) store8(res + c, x[i]);

@@ -11,9 +11,12 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, float* __restrict__ C, int M, int N, int K,
-                int lda, int ldw, int ldc) {
+                int lda, int ldw, int ldc, long long batch_a, long long batch_w, long long batch_c) {
   grid_dependency_wait();
   grid_dependency_launch();
+  A += (size_t)blockIdx.z * batch_a;     // one product per blockIdx.z (per head, for instance): operands `batch_*` apart
+  W += (size_t)blockIdx.z * batch_w;
+  C += (size_t)blockIdx.z * batch_c;
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -70,7 +73,24 @@ MS_EXPORT int ms_gemm_f32(const float* A, const float* W, float* C, int M, int N
   const int grid_m = (M + BM - 1) / BM, grid_n = (N + BN - 1) / BN;
   MS_REQUIRE(grid_m <= 65535, "gemm_f32: %d rows in one launch is too many", M);
   dim3 grid(grid_n, grid_m);
-  ms::launch(gemm_f32_kernel, grid, 256, 0, stream, A, W, C, M, N, K, lda, ldw, ldc);
+  ms::launch(gemm_f32_kernel, grid, 256, 0, stream, A, W, C, M, N, K, lda, ldw, ldc, 0LL, 0LL, 0LL);
   MS_CHECK_LAUNCH("gemm_f32");
+  return 0;
+}
+
+// `batch` products of the same sizes in one launch: C_b[M, N] = A_b[M, K] * W_b[N, K]^T with X_b = X + b * batch_x
+// (elements).  Rows may be strided (lda, ldw, ldc), so the operands can be slices of wider matrices: one head's
+// columns of a projection, one head's rows of an output.
+MS_EXPORT int ms_gemm_f32_batched(const float* A, const float* W, float* C, int M, int N, int K, int lda, int ldw, int ldc,
+                                  int batch, long long batch_a, long long batch_w, long long batch_c, cudaStream_t stream) {
+  if (M == 0 || N == 0 || batch == 0) return 0;
+  MS_REQUIRE(K > 0, "gemm_f32_batched: inner size must be positive, got %d", K);
+  MS_REQUIRE(lda >= K && ldw >= K && ldc >= N, "gemm_f32_batched: a row stride is smaller than its row (lda %d ldw %d ldc %d)",
+             lda, ldw, ldc);
+  const int grid_m = (M + BM - 1) / BM, grid_n = (N + BN - 1) / BN;
+  MS_REQUIRE(grid_m <= 65535 && batch <= 65535, "gemm_f32_batched: %d rows or %d products in one launch is too many", M, batch);
+  dim3 grid(grid_n, grid_m, batch);
+  ms::launch(gemm_f32_kernel, grid, 256, 0, stream, A, W, C, M, N, K, lda, ldw, ldc, batch_a, batch_w, batch_c);
+  MS_CHECK_LAUNCH("gemm_f32_batched");
   return 0;
 }

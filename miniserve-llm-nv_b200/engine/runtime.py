@@ -83,6 +83,9 @@ def build_runtime(model_dir: Union[str, Path, None], engine_config: Optional[Eng
         raise ValueError(f"max_model_len {max_model_len} exceeds the model's position limit {spec.max_positions}")
     page_size = engine_config.kv_block_size
     num_pages = engine_config.num_kv_blocks
+    if engine_config.max_model_len is None and spec.nominal_max_positions and num_pages is not None:
+        # a design without a position limit of its own: no request can be longer than the pool
+        max_model_len = min(max_model_len, num_pages * page_size)
     if num_pages is None:
         per_page = max(CacheStorage.bytes_per_page(model.cache_groups, page_size, dtype), 1)
         free, _total = torch.cuda.mem_get_info(device)
@@ -104,15 +107,27 @@ def build_runtime(model_dir: Union[str, Path, None], engine_config: Optional[Eng
 def _report_attention_kernels(model: DecoderModel, dtype: torch.dtype, page_size: int) -> list:
     """Says once per build which attention kernel each paged cache group gets, loudly where bfloat16 falls back
     to the general float32-arithmetic kernel (right, but many times slower than the tensor-core kernels)."""
-    from ..parts.base import PagedKVNeed
+    from ..parts.base import PagedKVNeed, PagedLatentNeed
 
     chosen = []
     for index, run in enumerate(model.spec.order):
         plan = model.run_caches[index]
         mixer = model.blocks[run.layer].mixer
-        if plan is None or not plan.writable or plan.slot != 0 or not isinstance(model.cache_groups[plan.group].need, PagedKVNeed):
+        if plan is None or not plan.writable or plan.slot != 0:
             continue
         need = model.cache_groups[plan.group].need
+        if isinstance(need, PagedLatentNeed):
+            heads = getattr(mixer, "num_heads", 1)
+            names = kernels.latent_attention_kernels(dtype, need.rank, need.rot, heads, page_size)
+            chosen.append(dict(group=plan.group, latent=need.rank, rotated=need.rot, window=need.window, **names))
+            slow = dtype == torch.bfloat16 and "general" in names.values()
+            log.log(logging.WARNING if slow else logging.INFO,
+                    "cache group %d (latent vectors of %d + %d numbers, %d heads, pages of %d): decode steps on the %s kernel, "
+                    "prompt portions on the %s kernel%s", plan.group, need.rank, need.rot, heads, page_size, names["decode"],
+                    names["prompt"], " (no tensor-core kernel is built for these sizes)" if slow else "")
+            continue
+        if not isinstance(need, PagedKVNeed):
+            continue
         n_q = getattr(mixer, "num_heads", need.num_kv_heads)
         modified = bool(getattr(mixer, "score_softcap", None)) or getattr(mixer, "score_bias_slopes", None) is not None
         names = kernels.attention_kernels(dtype, need.head_dim, n_q, need.num_kv_heads, page_size, modified)

@@ -64,7 +64,7 @@ def main(argv=None) -> int:
     args = build_cli_parser().parse_args(argv)
     import random
 
-    from .config.registry import read_config_json
+    from .config.registry import load_model_config
     from .engine.llm import LLM
     from .sampling.params import SamplingParams
     from .weights.random_init import write_random_model
@@ -76,7 +76,8 @@ def main(argv=None) -> int:
         config = json.loads(Path(args.random_config).read_text(encoding="utf-8"))
         model_dir = str(write_random_model(holder.name, config, args.weights_seed,
                                            "bfloat16" if args.dtype == "bfloat16" else "float32"))
-    vocab = int(read_config_json(model_dir)["vocab_size"])
+    architecture, model_config = load_model_config(model_dir)
+    vocab = architecture.build_spec(model_config).vocab_size
     prompts = [_ids(text) for text in args.prompt_ids]
     if args.prompt_lens:
         rng = random.Random(args.prompt_seed)

@@ -16,7 +16,7 @@ import torch
 
 from . import build
 
-ABI_VERSION = 5
+ABI_VERSION = 6
 log = logging.getLogger("miniserve_b200")
 _library: Optional[ctypes.CDLL] = None
 
@@ -119,8 +119,9 @@ def scale_softcap(x: torch.Tensor, scale: float = 1.0, cap: Optional[float] = No
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
-                out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
-    """Adds ``delta`` into the float32 ``residual`` (in place) and writes its RMSNorm to ``out``.
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None, delta2: Optional[torch.Tensor] = None) -> None:
+    """Adds ``delta`` into the float32 ``residual`` (in place) and writes its RMSNorm to ``out``.  With ``delta2``
+    (a second output of the same layer) the stream receives ``delta + delta2``, summed in float32.
 
     With ``rows`` (int32 ``[K]``) only those rows are normalised, into ``out [K, H]``, and
     the residual is left untouched.  ``weight`` may be float32 or bfloat16 whatever ``out`` is.
@@ -132,9 +133,14 @@ def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: t
     _want(weight, "weight", None, (hidden,))
     if delta is not None:
         _want(delta, "delta", out.dtype, residual.shape)
+    if delta2 is not None:
+        if delta is None:
+            delta, delta2 = delta2, None
+        else:
+            _want(delta2, "delta2", out.dtype, residual.shape)
     if rows is not None:
         _want(rows, "rows", torch.int32)
-    _check(library().ms_add_rmsnorm(_ptr(residual), _ptr(delta), _i(_code(out.dtype)), _ptr(weight),
+    _check(library().ms_add_rmsnorm(_ptr(residual), _ptr(delta), _ptr(delta2), _i(_code(out.dtype)), _ptr(weight),
                                     _i(_code(weight.dtype)), _ptr(rows), _ptr(out), _i(n_out), _i(hidden), _f(eps),
                                     _stream()))
 
@@ -149,13 +155,13 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
                                 _i(x.numel() // size), _i(size), _f(eps), _stream()))
 
 
-def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, cos_sin: torch.Tensor) -> None:
-    """``cos_sin[n, j] = (cos, sin)(positions[n] * inv_freq[j])`` in float32; cos_sin ``[N, half, 2]``."""
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, cos_sin: torch.Tensor, magnitude: float = 1.0) -> None:
+    """``cos_sin[n, j] = magnitude * (cos, sin)(positions[n] * inv_freq[j])`` in float32; cos_sin ``[N, half, 2]``."""
     n, half = positions.numel(), inv_freq.numel()
     _want(positions, "positions", torch.int32)
     _want(inv_freq, "inv_freq", torch.float32)
     _want(cos_sin, "cos_sin", torch.float32, (n, half, 2))
-    _check(library().ms_rope_table(_ptr(positions), _ptr(inv_freq), _ptr(cos_sin), _i(n), _i(half), _stream()))
+    _check(library().ms_rope_table(_ptr(positions), _ptr(inv_freq), _ptr(cos_sin), _i(n), _i(half), _f(magnitude), _stream()))
 
 
 def qk_norm_rope_append(qkv: torch.Tensor, slots: torch.Tensor, q_weight: Optional[torch.Tensor],
@@ -384,6 +390,189 @@ def decode_attention_fused(qkv: torch.Tensor, slots: torch.Tensor, q_weight: Opt
         _i(k_pool.shape[2]), _i(n_q), _i(n_kv), _i(head_dim), _f(scale), _i(window if window else 0), _ptr(out),
         _ptr(part_o), _ptr(part_lse), _i(splits), _i(n), _stream()))
 
+
+
+# --------------------------------------------------------------------------- latent attention
+
+
+def latent_prepare(proj: torch.Tensor, q_col: int, dkv_col: int, heads: int, dim: int, rot: int, rank: int,
+                   slots: torch.Tensor, norm_weight: torch.Tensor, eps: float, cos_sin: Optional[torch.Tensor],
+                   rot_dims: int, cache: torch.Tensor, q_full: torch.Tensor) -> None:
+    """What a latent-attention layer does between its input projection and its attention, for every token:
+    the latent ``proj[n, dkv_col : dkv_col + rank]`` is RMS-normed with ``norm_weight`` and, followed by the rotated
+    key part ``proj[n, dkv_col + rank : + rot]``, written to row ``slots[n]`` of ``cache [pages, page_size, rank + rot]``
+    (negative slot: no write); the rotated part of every query head (``proj[n, q_col + h (dim + rot) + dim : + rot]``)
+    is rotated into ``q_full[n, h, rank:]``.  The rotation acts on the first ``rot_dims`` entries of a rotated part,
+    entry i paired with i + rot_dims / 2, by ``cos_sin`` float32 ``[N, rot_dims / 2, 2]``."""
+    n, ld = proj.shape
+    _want(proj, "proj")
+    _want(slots, "slots", torch.int32, (n,))
+    _want(norm_weight, "norm_weight", None, (rank,))
+    _want(cache, "cache", proj.dtype)
+    if cache.dim() != 3 or cache.shape[2] != rank + rot:
+        raise KernelError(f"cache shape {tuple(cache.shape)} is not [pages, page_size, {rank + rot}]")
+    _want(q_full, "q_full", proj.dtype, (n, heads, rank + rot))
+    if q_col + heads * (dim + rot) > ld or dkv_col + rank + rot > ld:
+        raise KernelError(f"latent_prepare: the projections do not fit rows of {ld} numbers")
+    if cos_sin is not None:
+        _want(cos_sin, "cos_sin", torch.float32, (n, rot_dims // 2, 2))
+    else:
+        rot_dims = 0
+    _check(library().ms_latent_prepare(_ptr(proj), _i(_code(proj.dtype)), _i(ld), _i(q_col), _i(dkv_col), _i(heads), _i(dim),
+                                       _i(rot), _i(rank), _ptr(slots), _ptr(norm_weight), _i(_code(norm_weight.dtype)), _f(eps),
+                                       _ptr(cos_sin), _i(rot_dims), _ptr(cache), _ptr(q_full), _i(n), _stream()))
+
+
+def latent_attention_kernels(dtype: torch.dtype, rank: int, rot: int, heads: int, page_size: int) -> dict:
+    """Which kernel :func:`latent_attention` runs for these sizes, as :func:`attention_kernels` says it for keys and
+    values: ``{"decode": name, "prompt": name}`` with ``mma.sync`` or ``general``."""
+    if dtype == torch.bfloat16 and USE_LATENT_MMA and library().ms_latent_attention_mma_supports(_i(rank), _i(rot), _i(heads)):
+        return {"decode": "mma.sync", "prompt": "mma.sync"}
+    return {"decode": "general", "prompt": "general"}
+
+
+USE_LATENT_MMA = __import__("os").environ.get("MINISERVE_B200_LATENT_MMA", "1") == "1"
+
+
+def latent_attention(q_full: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor, request_of_token: torch.Tensor,
+                     positions: torch.Tensor, query_start: torch.Tensor, context_lens: torch.Tensor, max_query_len: int,
+                     max_context_len: int, rank: int, scale: float, window: Optional[int], out: torch.Tensor) -> None:
+    """Causal attention of every token's heads over its request's cached rows ``[c ; k_r]``: the score of head h is
+    ``q_full[n, h] . row * scale``, the result the softmax-weighted sum of the rows' first ``rank`` numbers.
+
+    q_full ``[N, H, rank + rot]``; cache of one layer ``[pages, page_size, rank + rot]``; out ``[N, H, rank]``; the
+    batch is described as for :func:`paged_attention`.  bfloat16 with sizes that the tensor-core kernel takes runs
+    there; everything else runs the general float32-arithmetic kernel."""
+    n, heads, dk = q_full.shape
+    _want(q_full, "q_full")
+    _want(cache, "cache", q_full.dtype)
+    if cache.dim() != 3 or cache.shape[2] != dk:
+        raise KernelError(f"cache shape {tuple(cache.shape)} is not [pages, page_size, {dk}]")
+    _want(out, "out", q_full.dtype, (n, heads, rank))
+    _want(block_tables, "block_tables", torch.int32)
+    _want(request_of_token, "request_of_token", torch.int32, (n,))
+    _want(positions, "positions", torch.int32, (n,))
+    n_requests = context_lens.numel()
+    _want(query_start, "query_start", torch.int32, (n_requests + 1,))
+    _want(context_lens, "context_lens", torch.int32, (n_requests,))
+    lib = library()
+    page_size = cache.shape[1]
+    if q_full.dtype == torch.bfloat16 and USE_LATENT_MMA and lib.ms_latent_attention_mma_supports(_i(rank), _i(dk - rank), _i(heads)):
+        splits = lib.ms_latent_attention_mma_splits(_i(rank), _i(dk - rank), _i(heads), _i(n_requests), _i(max_query_len),
+                                                    _i(max_context_len))
+        part_o = part_lse = None
+        if splits > 1:
+            part_o = torch.empty((n * heads * splits, rank), dtype=torch.float32, device=q_full.device)
+            part_lse = torch.empty((n * heads * splits,), dtype=torch.float32, device=q_full.device)
+        _check(lib.ms_latent_attention_mma(
+            _ptr(q_full), _ptr(cache), _ptr(block_tables), _i(block_tables.shape[1]), _ptr(query_start), _ptr(context_lens),
+            _i(page_size), _i(heads), _i(rank), _i(dk - rank), _f(scale), _i(window if window else 0), _ptr(out),
+            _ptr(part_o), _ptr(part_lse), _i(splits), _i(n_requests), _i(max_query_len), _i(n), _stream()))
+        return
+    _check(lib.ms_latent_attention_generic(
+        _ptr(q_full), _i(_code(q_full.dtype)), _ptr(cache), _ptr(block_tables), _i(block_tables.shape[1]),
+        _ptr(request_of_token), _ptr(positions), _i(page_size), _i(heads), _i(dk), _i(rank), _f(scale),
+        _i(window if window else 0), _ptr(out), _i(n), _stream()))
+
+
+def head_gate(x: torch.Tensor, gate: torch.Tensor, gate_col: int) -> None:
+    """In place on ``x [N, H, vdim]``: head h of token n is multiplied by ``sigmoid(gate[n, gate_col + h])``."""
+    n, heads, vdim = x.shape
+    _want(x, "x")
+    _want(gate, "gate", x.dtype)
+    if gate.dim() != 2 or gate.shape[0] != n or gate_col + heads > gate.shape[1]:
+        raise KernelError(f"head_gate: gate logits {tuple(gate.shape)} for {n} tokens of {heads} heads from column {gate_col}")
+    _check(library().ms_head_gate(_ptr(x), gate.data_ptr() + gate_col * gate.element_size(), _i(_code(x.dtype)),
+                                  _i(gate.shape[1]), _i(heads), _i(vdim), _i(n), _stream()))
+
+
+def linear_batched(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[b] = x[b] @ weight[b]^T`` for ``x [B, M, K]``, ``weight [B, N, K]``, ``out [B, M, N]``; ``x`` and ``out`` may be
+    strided views (a head's columns of wider rows) as long as their last dimension is dense.  float32 runs the
+    library's own FFMA kernel (one thread per output element, k ascending); bfloat16 goes to cuBLAS (``torch.bmm``)."""
+    b, m, k = x.shape
+    n = weight.shape[1]
+    if weight.shape != (b, n, k) or out.shape != (b, m, n) or x.stride(2) != 1 or out.stride(2) != 1 or not weight.is_contiguous():
+        raise KernelError(f"linear_batched: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if x.dtype == torch.float32:
+        if weight.dtype != torch.float32 or out.dtype != torch.float32 or not (x.is_cuda and weight.is_cuda and out.is_cuda):
+            raise KernelError("linear_batched: float32 CUDA tensors expected")
+        _check(library().ms_gemm_f32_batched(_ptr(x), _ptr(weight), _ptr(out), _i(m), _i(n), _i(k), _i(x.stride(1)), _i(k),
+                                             _i(out.stride(1)), _i(b), x.stride(0), n * k, out.stride(0), _stream()))
+        return
+    torch.bmm(x, weight.transpose(1, 2), out=out)
+
+
+# --------------------------------------------------------------------------- routed experts
+
+
+def router_topk(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], top: int, ids: torch.Tensor,
+                weights: torch.Tensor) -> None:
+    """Router of a mixture of experts: float32 logits ``x @ weight^T + bias`` (``weight`` float32 ``[E, width]``), the
+    ``top`` experts with the largest logits into ``ids`` int32 ``[N, top]`` (ties: the lower index) and the softmax over
+    those logits alone into ``weights`` float32 ``[N, top]``."""
+    n, width = x.shape
+    experts = weight.shape[0]
+    _want(x, "x")
+    _want(weight, "weight", torch.float32, (experts, width))
+    if bias is not None:
+        _want(bias, "bias", torch.float32, (experts,))
+    _want(ids, "ids", torch.int32, (n, top))
+    _want(weights, "weights", torch.float32, (n, top))
+    _check(library().ms_router_topk(_ptr(x), _i(_code(x.dtype)), _ptr(weight), _ptr(bias), _i(width), _i(experts), _i(top),
+                                    _ptr(ids), _ptr(weights), _i(n), _stream()))
+
+
+def expert_route(ids: torch.Tensor, experts: int, offsets: torch.Tensor, order: torch.Tensor, place: torch.Tensor) -> None:
+    """Sorts the (token, choice) pairs of ``ids [N, top]`` by expert: ``offsets`` int32 ``[E + 1]`` bounds each expert's
+    segment, ``order [N * top]`` lists the pairs (token * top + choice) segment by segment, ``place`` is its inverse."""
+    pairs = ids.numel()
+    _want(ids, "ids", torch.int32)
+    _want(offsets, "offsets", torch.int32, (experts + 1,))
+    _want(order, "order", torch.int32, (pairs,))
+    _want(place, "place", torch.int32, (pairs,))
+    _check(library().ms_expert_route(_ptr(ids), _i(pairs), _i(experts), _ptr(offsets), _ptr(order), _ptr(place), _stream()))
+
+
+def expert_linear(x: torch.Tensor, order: Optional[torch.Tensor], top: int, weight: torch.Tensor, out: torch.Tensor,
+                  offsets: torch.Tensor, relu_square: bool = False) -> None:
+    """One product per expert over its segment of the sorted pairs: ``out[i] = act(x[src(i)] @ weight[e]^T)`` for every
+    place ``i`` of expert ``e``'s segment, ``weight [E, N, K]``, ``out [pairs, N]``.  With ``order`` the rows are gathered from
+    the tokens (``src(i) = order[i] // top``, ``x [tokens, K]``), without it ``x [pairs, K]`` is in sorted order already.
+    ``relu_square``: ``act(z) = max(z, 0)^2``."""
+    experts, n, k = weight.shape
+    pairs = out.shape[0]
+    _want(x, "x", None)
+    _want(weight, "weight", x.dtype)
+    _want(out, "out", x.dtype, (pairs, n))
+    _want(offsets, "offsets", torch.int32, (experts + 1,))
+    if x.shape[1] != k or (order is None and x.shape[0] != pairs):
+        raise KernelError(f"expert_linear: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if order is not None:
+        _want(order, "order", torch.int32, (pairs,))
+    _check(library().ms_expert_linear(_ptr(x), _i(_code(x.dtype)), _i(k), _ptr(order), _i(top), _ptr(weight), _ptr(out), _i(n),
+                                      _ptr(offsets), _i(experts), _i(pairs), _i(n), _i(k), _i(1 if relu_square else 0), _stream()))
+
+
+def expert_combine(y: torch.Tensor, place: torch.Tensor, weights: torch.Tensor, shared: Optional[torch.Tensor],
+                   out: torch.Tensor) -> None:
+    """``out[n] = sum_k weights[n, k] * y[place[n * top + k]] (+ shared[n])``, summed in float32 in the order of k."""
+    n, top = weights.shape
+    width = out.shape[1]
+    _want(y, "y", out.dtype, (n * top, width))
+    _want(place, "place", torch.int32, (n * top,))
+    _want(weights, "weights", torch.float32)
+    _want(out, "out", None, (n, width))
+    if shared is not None:
+        _want(shared, "shared", out.dtype, (n, width))
+    _check(library().ms_expert_combine(_ptr(y), _i(_code(out.dtype)), _i(width), _ptr(place), _ptr(weights), _i(top), _ptr(shared),
+                                       _ptr(out), _i(width), _i(n), _stream()))
+
+
+def relu_square(x: torch.Tensor) -> None:
+    """In place: ``x = max(x, 0)^2``."""
+    _want(x, "x")
+    _check(library().ms_relu_square(_ptr(x), _i(_code(x.dtype)), x.numel(), _stream()))
 
 # --------------------------------------------------------------------------- matrix products
 

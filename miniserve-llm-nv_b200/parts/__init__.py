@@ -1,13 +1,14 @@
 """Layer parts and the model assembled from them."""
 
-from . import attention, block, feed_forward, norm, position  # noqa: F401  (register the built-in parts)
-from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, FoldedInput, NormFold, PagedKVNeed, ResidualAdd, ParamSpec, Part, StateNeed,
+from . import attention, block, experts, feed_forward, latent_attention, norm, position  # noqa: F401  (register the built-in parts)
+from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, PAGED_NEEDS, POSITIONS, FoldedInput, NormFold, PagedKVNeed, PagedLatentNeed,
+                   ResidualAdd, ParamSpec, Part, StateNeed,
                    register_block, register_feed_forward, register_mixer, register_norm, register_position)
-from .context import PagedKVView, StateView, StepContext
+from .context import PagedKVView, PagedLatentView, StateView, StepContext
 from .model import CacheGroup, DecoderModel, RunCache
 from .spec import LayerRun, LayerSpec, ModelSpec, PartSpec
 
-__all__ = ["BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "FoldedInput", "NormFold", "PagedKVNeed", "ResidualAdd", "ParamSpec", "Part",
-           "StateNeed", "register_block", "register_feed_forward", "register_mixer", "register_norm",
+__all__ = ["BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "PAGED_NEEDS", "POSITIONS", "FoldedInput", "NormFold", "PagedKVNeed",
+           "PagedLatentNeed", "PagedLatentView", "ResidualAdd", "ParamSpec", "Part", "StateNeed", "register_block", "register_feed_forward", "register_mixer", "register_norm",
            "register_position", "PagedKVView", "StateView", "StepContext", "CacheGroup", "DecoderModel", "RunCache",
            "LayerRun", "LayerSpec", "ModelSpec", "PartSpec"]

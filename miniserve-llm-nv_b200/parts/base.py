@@ -11,7 +11,8 @@ Families and the signature of their work method:
 norm            ``add_and_norm(residual, delta, out, rows=None)``: add ``delta`` (or nothing)
                 into the float32 residual stream in place, write the norm of the sum to ``out``
 position        ``tables(ctx)``: per-step device tables for the rotation; ``fused_args()``
-mixer           ``forward(x, ctx, cache) -> y``; ``cache_need()`` says what ``cache`` must be
+mixer           ``forward(x, ctx, cache) -> y``; ``cache_need()`` says what ``cache`` must be (paged keys
+                and values, paged latent vectors, a fixed-size state, or nothing)
 feed_forward    ``forward(x, ctx) -> y``
 block           ``forward(residual, delta, ctx, cache) -> delta``: arranges the four above
 ==============  ==========================================================================
@@ -42,7 +43,8 @@ class ParamSpec:
 
     ``kind``: ``"matrix"`` is kept in the compute type (bfloat16 or float32); ``"vector"``
     (norm weights and the like) keeps 32 bits if the checkpoint stores 32 bits and takes the
-    compute type otherwise; ``"table"`` is an integer table kept as int32.
+    compute type otherwise; ``"matrix_f32"`` (a router) is a matrix kept in float32 whatever the
+    compute type; ``"table"`` is an integer table kept as int32.
     """
 
     name: str
@@ -57,6 +59,19 @@ class PagedKVNeed:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class PagedLatentNeed:
+    """The mixer keeps ONE vector per token in pages: a latent of ``rank`` numbers, from which the keys and values of
+    all heads are computed, followed by ``rot`` numbers of a rotated key part that all heads share."""
+
+    rank: int
+    rot: int
+    window: Optional[int] = None
+
+
+PAGED_NEEDS = (PagedKVNeed, PagedLatentNeed)     # needs whose cache is paged: block tables, slots, pages given back
 
 
 @dataclass(frozen=True)

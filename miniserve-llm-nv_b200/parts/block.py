@@ -1,5 +1,6 @@
 """Block arrangements.  ``pre_norm``: ``h += mixer(norm(h)); h += feed_forward(norm(h))``
-(miniserve/model/qwen3.py:336-346).
+(miniserve/model/qwen3.py:336-346).  ``parallel``: one norm whose output both sublayers read,
+``h += mixer(norm(h)) + feed_forward(norm(h))``; a layer without a feed-forward is ``h += mixer(norm(h))``.
 
 The residual stream ``h`` is float32 and is updated in place.  A block receives the stream
 together with a *pending* ``delta`` that has not been added yet (the previous block's
@@ -24,7 +25,8 @@ from .. import kernels
 from .base import FoldedInput, NormFold, ResidualAdd, register_block
 from .context import StepContext
 
-Pending = Union[None, torch.Tensor, FoldedInput]     # what a block hands on: nothing, an output still to add, or a folded input
+# what a block hands on: nothing, an output still to add (or two, whose float32 sum is to be added), or a folded input
+Pending = Union[None, torch.Tensor, tuple, FoldedInput]
 
 
 def fold_between(producer, norm, consumer, ctx: StepContext) -> Optional[tuple]:
@@ -89,3 +91,31 @@ class PreNormBlock:
         if adds_into_stream(self.feed_forward, ctx):
             return self.feed_forward.forward(normed, ctx, fold=ResidualAdd(residual))
         return self.feed_forward.forward(normed, ctx)
+
+
+@register_block("parallel")
+class ParallelBlock:
+    """``x <- x + (mixer(h) + feed_forward(h))`` with ``h = norm(x)``: one norm per layer, read by both sublayers.
+
+    Both outputs are handed on unadded, as a pair: the norm of the block that follows (or the model's last norm)
+    adds their float32 sum into the stream as it reads it, so the sum never passes through the compute type.
+    """
+
+    def __init__(self, *, mixer, feed_forward, mixer_norm, feed_forward_norm=None) -> None:
+        if feed_forward_norm is not None:
+            raise ValueError("a parallel block has one norm; its feed-forward reads the mixer's input")
+        self.mixer, self.feed_forward, self.mixer_norm = mixer, feed_forward, mixer_norm
+
+    def parts(self):
+        return [part for part in (self.mixer_norm, self.mixer, self.feed_forward) if part is not None]
+
+    def forward(self, residual: torch.Tensor, pending: Pending, ctx: StepContext, cache: Any) -> Pending:
+        if isinstance(pending, FoldedInput):
+            raise TypeError("a parallel block takes its input from its own norm")
+        # (a buffer of its own: the pending outputs of the layer before live in the parts' buffers until they are added here)
+        normed = ctx.buffer("parallel.normed", tuple(residual.shape), ctx.dtype)
+        self.mixer_norm.add_and_norm(residual, pending, normed)
+        mixed = self.mixer.forward(normed, ctx, cache)
+        if self.feed_forward is None:
+            return mixed
+        return mixed, self.feed_forward.forward(normed, ctx)

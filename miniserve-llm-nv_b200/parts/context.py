@@ -34,6 +34,18 @@ class PagedKVView:
 
 
 @dataclass
+class PagedLatentView:
+    """One run's latent vectors: a pool ``[pages, page_size, rank + rot]`` of its layer; ``block_tables``, ``slots`` and
+    ``writable`` as in :class:`PagedKVView`."""
+
+    pool: torch.Tensor
+    block_tables: torch.Tensor
+    slots: torch.Tensor
+    page_size: int
+    writable: bool = True
+
+
+@dataclass
 class StateView:
     """One run's fixed-size state: ``states[slot]`` belongs to the request in that state slot."""
 

@@ -13,7 +13,7 @@ from typing import Any, Optional, Union
 import torch
 
 from .. import kernels
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, PagedKVNeed, ParamSpec, StateNeed
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, PagedKVNeed, PagedLatentNeed, ParamSpec, StateNeed
 from .context import StepContext
 from .spec import ModelSpec
 
@@ -22,7 +22,7 @@ from .spec import ModelSpec
 class CacheGroup:
     """Runs whose caches have the same form share one group (its own pools and page tables)."""
 
-    need: Union[PagedKVNeed, StateNeed]
+    need: Union[PagedKVNeed, PagedLatentNeed, StateNeed]
     n_slots: int          # runs that own a cache in this group
 
 
@@ -39,9 +39,9 @@ class DecoderModel:
         self.blocks = []
         for layer in spec.layers:
             mixer = MIXERS.build(layer.mixer, prefix=layer.prefix)
-            feed_forward = FEED_FORWARDS.build(layer.feed_forward, prefix=layer.prefix)
+            feed_forward = None if layer.feed_forward is None else FEED_FORWARDS.build(layer.feed_forward, prefix=layer.prefix)
             mixer_norm = NORMS.build(layer.mixer_norm, prefix=layer.prefix)
-            feed_forward_norm = NORMS.build(layer.feed_forward_norm, prefix=layer.prefix)
+            feed_forward_norm = None if layer.feed_forward_norm is None else NORMS.build(layer.feed_forward_norm, prefix=layer.prefix)
             self.blocks.append(BLOCKS.build(layer.block, mixer=mixer, feed_forward=feed_forward,
                                             mixer_norm=mixer_norm, feed_forward_norm=feed_forward_norm))
         self.final_norm = NORMS.build(spec.final_norm)

@@ -23,14 +23,19 @@ class RMSNorm(Part):
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
         self.weight = tensors[self.name]
 
-    def add_and_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor], out: torch.Tensor,
+    def add_and_norm(self, residual: torch.Tensor, delta, out: torch.Tensor,
                      rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``residual += delta`` (float32, in place; skipped when ``delta`` is None), ``out = norm(residual)``.
+        ``delta`` may be a pair of tensors (a block whose mixer and feed-forward read the same input hands on both
+        outputs): the stream then receives their float32 sum.
 
         With ``rows`` only those rows are normalised into ``out [len(rows), size]`` and the
         residual stays as it is.
         """
-        kernels.add_rmsnorm(residual, delta, self.weight, self.eps, out, rows)
+        second = None
+        if isinstance(delta, tuple):
+            delta, second = delta
+        kernels.add_rmsnorm(residual, delta, self.weight, self.eps, out, rows, second)
         return out
 
     def fold(self) -> tuple[torch.Tensor, float]:

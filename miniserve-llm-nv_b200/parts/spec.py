@@ -28,9 +28,9 @@ class LayerSpec:
 
     prefix: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]           # None: the layer has no feed-forward
     mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward_norm: Optional[PartSpec]      # None: the block has one norm (``parallel``)
     block: PartSpec = PartSpec("pre_norm")
 
 
@@ -57,6 +57,9 @@ class ModelSpec:
     final_norm: PartSpec
     output_name: Optional[str]      # None: the output matrix is the embedding table (tied)
     max_positions: int
+    # True where the architecture has no position limit of its own and `max_positions` is only the engine's bound:
+    # without an explicit `max_model_len` a runtime then takes the size of its page pool as the limit.
+    nominal_max_positions: bool = False
     # Names that may be present in a checkpoint without being used (a stored copy of a tied matrix).
     optional_names: Sequence[str] = ()
     # The frame around the layers: embeddings are multiplied by `embedding_scale` as they enter the residual

@@ -33,7 +33,7 @@ from pathlib import Path
 from typing import Optional
 
 DEFAULT_PAGE_SIZE = 16   # divides 64, the granularity in which --max-tokens counts a request
-MAX_LIVE_REQUESTS = 8
+MAX_LIVE_REQUESTS = 4    # state slots: a trace never has more requests live at a time unless --max-requests says so
 
 
 class TraceError(RuntimeError):

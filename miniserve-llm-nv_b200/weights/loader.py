@@ -9,7 +9,8 @@ names, the unexpected names and the wrong shapes.
 
 Kept types: a ``matrix`` takes the compute type (bfloat16 stays bfloat16; float32 compute
 widens exactly); a ``vector`` stored in 32 bits stays float32 even when computing in
-bfloat16; a ``table`` of integers becomes int32.  When the output matrix is tied to the
+bfloat16; a ``matrix_f32`` (a router) is widened to float32 always; a ``table`` of integers
+becomes int32.  When the output matrix is tied to the
 embedding and the checkpoint still stores it, the stored copy must equal the embedding bit for
 bit (loader.py:132-152).
 """
@@ -74,6 +75,8 @@ def weight_files(folder: Path) -> list[Path]:
 def kept_dtype(spec: ParamSpec, stored: torch.dtype, compute: torch.dtype) -> torch.dtype:
     if spec.kind == "table":
         return torch.int32
+    if spec.kind == "matrix_f32":
+        return torch.float32
     if spec.kind == "vector" and stored in (torch.float32, torch.float64):
         return torch.float32
     return compute

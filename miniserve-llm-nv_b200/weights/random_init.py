@@ -50,7 +50,7 @@ def random_tensors_on_device(specs, seed: int, dtype: torch.dtype, device, matri
             continue
         value = torch.randn(spec.shape, generator=generator, device=device, dtype=torch.float32)
         value = 1.0 + value * vector_std if spec.kind == "vector" else value * matrix_std
-        tensors[spec.name] = value.to(dtype)
+        tensors[spec.name] = value.to(torch.float32 if spec.kind == "matrix_f32" else dtype)
     return tensors
 
 

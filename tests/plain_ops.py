@@ -27,7 +27,9 @@ def embedding(tokens, table, out, scale=1.0):
     out.copy_((scale * table[tokens.long()].double()).to(out.dtype))
 
 
-def add_rmsnorm(residual, delta, weight, eps, out, rows=None):
+def add_rmsnorm(residual, delta, weight, eps, out, rows=None, delta2=None):
+    if delta2 is not None:
+        delta = delta2 if delta is None else (delta.double() + delta2.double())
     if rows is None:
         if delta is not None:
             residual += delta.to(residual.dtype)
@@ -47,10 +49,10 @@ def rmsnorm(x, weight, eps, out):
     out.copy_(y.to(out.dtype))
 
 
-def rope_table(positions, inv_freq, cos_sin):
+def rope_table(positions, inv_freq, cos_sin, magnitude=1.0):
     angles = (positions.to(torch.float32)[:, None] * inv_freq[None, :]).double()
-    cos_sin[..., 0] = angles.cos().to(cos_sin.dtype)
-    cos_sin[..., 1] = angles.sin().to(cos_sin.dtype)
+    cos_sin[..., 0] = (magnitude * angles.cos()).to(cos_sin.dtype)
+    cos_sin[..., 1] = (magnitude * angles.sin()).to(cos_sin.dtype)
 
 
 def rotate(x, cos_sin, rotary_dim, interleaved):
@@ -188,15 +190,118 @@ def sample(logits, records, slot_of_row, draw_index, out):
                                       int(draw_index[row]))
 
 
+# --------------------------------------------------------------------------- latent attention
+
+
+def latent_prepare(proj, q_col, dkv_col, heads, dim, rot, rank, slots, norm_weight, eps, cos_sin, rot_dims, cache, q_full):
+    n = proj.shape[0]
+    p = proj.double()
+
+    def turn(x):                       # x [n, ..., rot]: the first rot_dims entries rotated, entry i with i + rot_dims / 2
+        if cos_sin is None or not rot_dims:
+            return x
+        half = rot_dims // 2
+        shape = [n] + [1] * (x.dim() - 2) + [half]
+        cos, sin = cos_sin[..., 0].double().view(shape), cos_sin[..., 1].double().view(shape)
+        out = x.clone()
+        u, v = x[..., :half], x[..., half:rot_dims]
+        out[..., :half], out[..., half:rot_dims] = u * cos - v * sin, v * cos + u * sin
+        return out
+
+    q = p[:, q_col:q_col + heads * (dim + rot)].view(n, heads, dim + rot)
+    q_full[:, :, rank:] = turn(q[..., dim:]).to(q_full.dtype)
+    latent = p[:, dkv_col:dkv_col + rank]
+    latent = norm_weight.double() * (latent * torch.rsqrt(latent.pow(2).mean(-1, keepdim=True) + eps))
+    rows = torch.cat([latent, turn(p[:, dkv_col + rank:dkv_col + rank + rot])], dim=1).to(cache.dtype)
+    flat = cache.view(-1, rank + rot)
+    for token in range(n):
+        if int(slots[token]) >= 0:
+            flat[int(slots[token])] = rows[token]
+
+
+def latent_attention(q_full, cache, block_tables, request_of_token, positions, query_start, context_lens, max_query_len,
+                     max_context_len, rank, scale, window, out):
+    n, heads, dk = q_full.shape
+    page_size = cache.shape[1]
+    for token in range(n):
+        pos = int(positions[token])
+        table = block_tables[int(request_of_token[token])]
+        first = max(0, pos - window + 1) if window else 0
+        keys = torch.arange(first, pos + 1)
+        rows = cache[table[(keys // page_size).long()].long(), (keys % page_size).long()].double()     # [keys, dk]
+        for head in range(heads):
+            p = torch.softmax((rows @ q_full[token, head].double()) * scale, dim=0)
+            out[token, head] = (p @ rows[:, :rank]).to(out.dtype)
+
+
+def head_gate(x, gate, gate_col):
+    heads = x.shape[1]
+    x.copy_((x.double() * torch.sigmoid(gate[:, gate_col:gate_col + heads].double())[:, :, None]).to(x.dtype))
+
+
+def linear_batched(x, weight, out):
+    out.copy_(torch.einsum("bmk,bnk->bmn", x.double(), weight.double()).to(out.dtype))
+
+
+# --------------------------------------------------------------------------- routed experts
+
+
+def router_topk(x, weight, bias, top, ids, weights):
+    logits = x.double() @ weight.double().T
+    if bias is not None:
+        logits = logits + bias.double()
+    ranked = logits.sort(dim=1, descending=True, stable=True)
+    ids.copy_(ranked.indices[:, :top].to(ids.dtype))
+    weights.copy_(torch.softmax(ranked.values[:, :top], dim=1).to(weights.dtype))
+
+
+def expert_route(ids, experts, offsets, order, place):
+    flat = ids.reshape(-1).long()
+    sorted_pairs = torch.sort(flat, stable=True).indices
+    order.copy_(sorted_pairs.to(order.dtype))
+    place[sorted_pairs] = torch.arange(flat.numel(), dtype=place.dtype)
+    counts = torch.bincount(flat, minlength=experts)
+    offsets[0] = 0
+    offsets[1:] = counts.cumsum(0).to(offsets.dtype)
+
+
+def expert_linear(x, order, top, weight, out, offsets, relu_square=False):
+    for e in range(weight.shape[0]):
+        lo, hi = int(offsets[e]), int(offsets[e + 1])
+        if hi == lo:
+            continue
+        rows = x[(order[lo:hi] // top).long()] if order is not None else x[lo:hi]
+        y = rows.double() @ weight[e].double().T
+        if relu_square:
+            y = y.clamp(min=0).pow(2)
+        out[lo:hi] = y.to(out.dtype)
+
+
+def expert_combine(y, place, weights, shared, out):
+    n, top = weights.shape
+    picked = y.double()[place.long()].view(n, top, -1)
+    total = (weights.double()[:, :, None] * picked).sum(dim=1)
+    if shared is not None:
+        total = total + shared.double()
+    out.copy_(total.to(out.dtype))
+
+
+def relu_square(x):
+    x.copy_(x.double().clamp(min=0).pow(2).to(x.dtype))
+
+
 def install(monkeypatch) -> None:
     """Puts the functions above in place of the kernel bindings (CPU tests of host logic only)."""
     import miniserve_b200  # noqa: F401
     from miniserve_b200 import kernels
 
     for name in ("embedding", "add_rmsnorm", "rmsnorm", "rope_table", "qk_norm_rope_append", "silu_mul",
-                 "paged_attention", "linear", "gated_linear", "gated_up", "sample", "scale_softcap"):
+                 "paged_attention", "linear", "gated_linear", "gated_up", "sample", "scale_softcap", "latent_prepare",
+                 "latent_attention", "head_gate", "linear_batched", "router_topk", "expert_route", "expert_linear",
+                 "expert_combine", "relu_square"):
         monkeypatch.setattr(kernels, name, globals()[name])
     monkeypatch.setattr(kernels, "attention_kernels", lambda *sizes: {"decode": "plain", "prompt": "plain"})
+    monkeypatch.setattr(kernels, "latent_attention_kernels", lambda *sizes: {"decode": "plain", "prompt": "plain"})
     # norms folded into the products around them: offered for steps of up to eight rows and for steps of many
     # (here: 24 and more), as on the device, with the two layouts of the sums of squares
     monkeypatch.setattr(kernels, "linear_residual", linear_residual)
