@@ -79,8 +79,9 @@ def rotate(x, positions, rot):
     return out
 
 
-def latent_attention(h, w, prefix, mixer, eps, positions):
-    """The mixer on a whole sequence; every token's key and value are recomputed from its latent."""
+def latent_attention(h, w, prefix, mixer, eps, positions, window=None):
+    """The mixer on a whole sequence; every token's key and value are recomputed from its latent.  (``window``: a query
+    sees only the last ``window`` keys; the design itself has none, the engine's part takes one as an option.)"""
     n = h.shape[0]
     heads, dim, rot_dim = int(mixer["heads"]), int(mixer["dim"]), int(mixer["rot_dim"])
     vdim, rank = int(mixer["vdim"]), int(mixer["kv_rank"])
@@ -91,8 +92,10 @@ def latent_attention(h, w, prefix, mixer, eps, positions):
     k_rot = rotate(down[:, rank:], positions, mixer["rot"])                   # one rotated key part for all heads
     k_plain = (latent @ w[prefix + "uk"].T).view(n, heads, dim)
     values = (latent @ w[prefix + "uv"].T).view(n, heads, vdim)
-    gate = torch.sigmoid(h @ w[prefix + "g"].T)                               # [n, heads]
+    gate = torch.sigmoid(h @ w[prefix + "g"].T) if prefix + "g" in w else torch.ones(n, heads, dtype=h.dtype)
     visible = positions[None, :] <= positions[:, None]
+    if window:
+        visible = visible & (positions[None, :] > positions[:, None] - window)
     out = torch.zeros(n, heads, vdim, dtype=h.dtype)
     for head in range(heads):
         scores = (q_plain[:, head] @ k_plain[:, head].T + q_rot[:, head] @ k_rot.T) * float(mixer["scale"])
