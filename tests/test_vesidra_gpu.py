@@ -25,7 +25,8 @@ DTYPES = [torch.float32, torch.bfloat16]
 
 
 def bound_of(dtype, expected):
-    return (3e-5 if dtype in ("float32", torch.float32) else 4e-2) * max(1.0, float(expected.abs().max()))
+    # (seen on B200: at most 0.13 of the float32 bound and 0.23 of the bfloat16 bound)
+    return (8e-6 if dtype in ("float32", torch.float32) else 1e-2) * max(1.0, float(expected.abs().max()))
 
 
 # --------------------------------------------------------------------------- kernels alone
@@ -249,8 +250,12 @@ def test_latent_attention_part_far_keys_and_edges(dtype, case, window):
     total = 333
     x = rand((total, width), dtype, 50)
     quiet_x = x.clone()
-    loud = [5, 250] if window is None else [total - 40 - window, total - 40 - window + 1, total - 3 - window, total - 3 - window + 1]
-    x[loud] *= 25.0
+    # (two keys of the same loudness in one query's sight would compete, and bfloat16 rounds scores of 50 by 0.2: the
+    # keys just outside are the loudest, so that letting one in would show most)
+    loud = {5: 25.0, 250: 5.0} if window is None else {total - 40 - window: 25.0, total - 40 - window + 1: 5.0,
+                                                       total - 3 - window: 25.0, total - 3 - window + 1: 5.0}
+    for token, factor in loud.items():
+        x[token] *= factor
     harness = Harness([part.cache_need()], dtype, page_size=8, num_pages=64, max_len=512)
     cuts = [(0, 3), (3, 5), (5, 130), (130, 131), (131, 290)] + [(i, i + 1) for i in range(290, total)]
     got = []
