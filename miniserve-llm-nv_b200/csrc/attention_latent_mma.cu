@@ -1,15 +1,307 @@
-// Tensor-core form of the latent attention (placeholder while the kernel is brought up: it takes no sizes yet, so
-// every call runs the general kernel).
+// Latent attention on the tensor cores (bfloat16, mma.sync.m16n8k16, float32 scores and sums).
+//
+// All heads of a token attend to the same cached rows [c ; k_r] of D_K numbers, whose first D_V numbers are also the
+// values (attention_latent.cu), so a request's query rows (token-major, head-minor: row = token * H + head) form ONE
+// matrix Q [tokens * H, D_K] against ONE key matrix K [context, D_K] and value matrix V = K[:, :D_V]: a key tile
+// is fetched once into shared memory and serves as the B operand of both products (row-major for Q K^T, read
+// transposed by ldmatrix for P V).  The causal mask follows the row's token: row r sees keys up to
+// context - tokens + r / H.
+//
+// A block owns 16 * ROWW query rows of one request.  Each group of 16 rows has VS warps that share the rows and split the
+// D_V value columns between them (each computes the scores of the whole key tile itself; with D_V = 512 one warp's
+// share of the output, 16 x 512 float32, would not fit its registers).  Key tiles of 32 rows go through two buffers
+// filled by cp.async, the next on its way while this one is multiplied.  Shared-memory rows are D_K + 8 elements
+// apart, which puts the eight rows of an ldmatrix into eight different bank groups for every D_K that is a multiple
+// of 16.
+//
+// Prompt portions run with ROWW = 4 and all keys in one block; steps of single tokens run with ROWW = 1 (H rows per
+// request: one tile of 16 for up to 16 heads) and the keys cut into `splits` ranges over blockIdx.z, whose partial
+// results (float32, with the base-2 logarithm of their sums) the shared merge kernel adds.
 #include "common.cuh"
+#include "mma_common.cuh"
 
-MS_EXPORT int ms_latent_attention_mma_supports(int rank, int rot, int heads) { return 0; }
+namespace ms {
 
+constexpr int LBN = 32;       // keys per tile
+
+template <int DV, int VS, int ROWW>
+__global__ void __launch_bounds__(32 * VS * ROWW)
+latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_full, const __nv_bfloat16* __restrict__ cache,
+                            const int* __restrict__ block_tables, int table_stride, const int* __restrict__ query_start,
+                            const int* __restrict__ context_lens, int page_size, int heads, int dk, float scale_log2,
+                            int window, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
+                            float* __restrict__ part_lse, int splits) {
+  constexpr int DVW = DV / VS;          // value columns of one warp
+  constexpr int THREADS = 32 * VS * ROWW;
+  static_assert(DVW % 16 == 0, "a warp's share of the values must be a multiple of 16 columns");
+  extern __shared__ __align__(16) unsigned char latent_smem[];
+  grid_dependency_wait();
+  grid_dependency_launch();
+  const int dkp = dk + 8;
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(latent_smem);     // [16 * ROWW][dkp]
+  __nv_bfloat16* k_s = q_s + 16 * ROWW * dkp;                             // [2][LBN][dkp]
+  const int req = blockIdx.y, split = blockIdx.z;
+  const int q0 = query_start[req], q_len = query_start[req + 1] - q0, ctx = context_lens[req];
+  const int rows = q_len * heads;
+  const int m0 = blockIdx.x * 16 * ROWW;
+  if (m0 >= rows) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wr = warp / VS, wv = warp % VS;
+  const int* table = block_tables + (size_t)req * table_stride;
+
+  // the keys this block walks: up to the position of its last row, from the window's start of its first
+  const int last_row = min(m0 + 16 * ROWW, rows) - 1;
+  const int pos_last = ctx - q_len + last_row / heads;
+  const int pos_first = ctx - q_len + m0 / heads;
+  const int key_begin = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
+  const int tile_begin = key_begin / LBN, tile_end = pos_last / LBN + 1;
+  const int per_split = (tile_end - tile_begin + splits - 1) / splits;
+  const int t_begin = tile_begin + split * per_split;
+  const int t_end = min(tile_end, t_begin + per_split);
+
+  const int chunks = dk >> 3;           // 16-byte pieces per row
+  auto load_keys = [&](int tile, int buffer) {
+    __nv_bfloat16* dst = k_s + (size_t)buffer * LBN * dkp;
+    for (int i = tid; i < LBN * chunks; i += THREADS) {
+      const int r = i / chunks, c = i % chunks;
+      const int key = tile * LBN + r;
+      const bool valid = key <= pos_last;
+      const int page = valid ? table[key / page_size] : 0;
+      const __nv_bfloat16* src = cache + ((size_t)page * page_size + (valid ? key % page_size : 0)) * dk + c * 8;
+      cp_async_16(dst + r * dkp + c * 8, src, valid);
+    }
+  };
+  if (t_begin < t_end) {
+    const __nv_bfloat16* q_rows = q_full + ((size_t)q0 * heads + m0) * dk;
+    for (int i = tid; i < 16 * ROWW * chunks; i += THREADS) {
+      const int r = i / chunks, c = i % chunks;
+      cp_async_16(q_s + r * dkp + c * 8, q_rows + (size_t)r * dk + c * 8, m0 + r < rows);
+    }
+    load_keys(t_begin, 0);
+  }
+  cp_async_commit();
+
+  // this thread's two rows of the 16: lane / 4 and lane / 4 + 8
+  const int row_a = m0 + wr * 16 + (lane >> 2), row_b = row_a + 8;
+  const int pos_a = row_a < rows ? ctx - q_len + row_a / heads : -1;     // -1: no key is visible (a row beyond the request's)
+  const int pos_b = row_b < rows ? ctx - q_len + row_b / heads : -1;
+  const int low_a = window > 0 ? pos_a - window : -2147483647, low_b = window > 0 ? pos_b - window : -2147483647;
+  float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+  float o[DVW / 8][4];
+#pragma unroll
+  for (int i = 0; i < DVW / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+  for (int tile = t_begin; tile < t_end; ++tile) {
+    const int buffer = (tile - t_begin) & 1;
+    if (tile + 1 < t_end) load_keys(tile + 1, buffer ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const __nv_bfloat16* kt = k_s + (size_t)buffer * LBN * dkp;
+
+    float s[LBN / 8][4];
+#pragma unroll
+    for (int i = 0; i < LBN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+    for (int kc = 0; kc < (dk >> 4); ++kc) {
+      unsigned a[4];
+      ldmatrix_x4(a, q_s + (wr * 16 + (lane & 15)) * dkp + kc * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int np = 0; np < LBN / 16; ++np) {
+        unsigned b[4];
+        ldmatrix_x4(b, kt + (np * 16 + (lane & 7) + (lane >> 4) * 8) * dkp + kc * 16 + ((lane >> 3) & 1) * 8);
+        mma_bf16(s[2 * np], a, b[0], b[1]);
+        mma_bf16(s[2 * np + 1], a, b[2], b[3]);
+      }
+    }
+    // mask, running maximum and sum (base 2)
+    float max_a = -INFINITY, max_b = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < LBN / 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int key = tile * LBN + nt * 8 + (lane & 3) * 2 + e;
+        s[nt][e] = (key <= pos_a && key > low_a) ? s[nt][e] * scale_log2 : -INFINITY;
+        s[nt][2 + e] = (key <= pos_b && key > low_b) ? s[nt][2 + e] * scale_log2 : -INFINITY;
+        max_a = fmaxf(max_a, s[nt][e]);
+        max_b = fmaxf(max_b, s[nt][2 + e]);
+      }
+    }
+    max_a = fmaxf(max_a, __shfl_xor_sync(0xffffffffu, max_a, 1));
+    max_a = fmaxf(max_a, __shfl_xor_sync(0xffffffffu, max_a, 2));
+    max_b = fmaxf(max_b, __shfl_xor_sync(0xffffffffu, max_b, 1));
+    max_b = fmaxf(max_b, __shfl_xor_sync(0xffffffffu, max_b, 2));
+    const float new_a = fmaxf(m_a, max_a), new_b = fmaxf(m_b, max_b);
+    const float use_a = new_a == -INFINITY ? 0.f : new_a, use_b = new_b == -INFINITY ? 0.f : new_b;   // (nothing seen yet: all p are 0)
+    const float corr_a = exp2f(m_a - use_a), corr_b = exp2f(m_b - use_b);
+    m_a = new_a;
+    m_b = new_b;
+    float sum_a = 0.f, sum_b = 0.f;
+    unsigned p[LBN / 16][4];
+#pragma unroll
+    for (int nt = 0; nt < LBN / 8; ++nt) {
+      const float p0 = exp2f(s[nt][0] - use_a), p1 = exp2f(s[nt][1] - use_a);
+      const float p2 = exp2f(s[nt][2] - use_b), p3 = exp2f(s[nt][3] - use_b);
+      sum_a += p0 + p1;
+      sum_b += p2 + p3;
+      p[nt >> 1][(nt & 1) * 2] = pack_bf16(p0, p1);
+      p[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+    l_a = l_a * corr_a + sum_a;
+    l_b = l_b * corr_b + sum_b;
+#pragma unroll
+    for (int i = 0; i < DVW / 8; ++i) {
+      o[i][0] *= corr_a;
+      o[i][1] *= corr_a;
+      o[i][2] *= corr_b;
+      o[i][3] *= corr_b;
+    }
+    // O += P V with V the first D_V columns of the same tile, read transposed
+#pragma unroll
+    for (int kk = 0; kk < LBN / 16; ++kk) {
+#pragma unroll
+      for (int np = 0; np < DVW / 16; ++np) {
+        unsigned b[4];
+        ldmatrix_x4_trans(b, kt + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * dkp + wv * DVW + np * 16 + (lane >> 4) * 8);
+        mma_bf16(o[2 * np], p[kk], b[0], b[1]);
+        mma_bf16(o[2 * np + 1], p[kk], b[2], b[3]);
+      }
+    }
+    __syncthreads();        // the buffer is refilled by the loads of the next iteration
+  }
+  cp_async_wait<0>();
+
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+  const size_t item_a = (size_t)q0 * heads + row_a, item_b = (size_t)q0 * heads + row_b;
+  const int col0 = wv * DVW + (lane & 3) * 2;
+  if (splits == 1) {
+    const float inv_a = l_a > 0.f ? 1.f / l_a : 0.f, inv_b = l_b > 0.f ? 1.f / l_b : 0.f;
+#pragma unroll
+    for (int i = 0; i < DVW / 8; ++i) {
+      if (row_a < rows)
+        *reinterpret_cast<__nv_bfloat162*>(out + item_a * DV + col0 + i * 8) = __floats2bfloat162_rn(o[i][0] * inv_a, o[i][1] * inv_a);
+      if (row_b < rows)
+        *reinterpret_cast<__nv_bfloat162*>(out + item_b * DV + col0 + i * 8) = __floats2bfloat162_rn(o[i][2] * inv_b, o[i][3] * inv_b);
+    }
+    return;
+  }
+  // partial result of this split: its own softmax-weighted mean, and log2 of its sum of 2^score
+  const float inv_a = l_a > 0.f ? 1.f / l_a : 0.f, inv_b = l_b > 0.f ? 1.f / l_b : 0.f;
+  if (row_a < rows) {
+    float* dst = part_o + (item_a * splits + split) * DV + col0;
+#pragma unroll
+    for (int i = 0; i < DVW / 8; ++i) *reinterpret_cast<float2*>(dst + i * 8) = make_float2(o[i][0] * inv_a, o[i][1] * inv_a);
+    if (wv == 0 && (lane & 3) == 0) part_lse[item_a * splits + split] = l_a > 0.f ? m_a + log2f(l_a) : -INFINITY;
+  }
+  if (row_b < rows) {
+    float* dst = part_o + (item_b * splits + split) * DV + col0;
+#pragma unroll
+    for (int i = 0; i < DVW / 8; ++i) *reinterpret_cast<float2*>(dst + i * 8) = make_float2(o[i][2] * inv_b, o[i][3] * inv_b);
+    if (wv == 0 && (lane & 3) == 0) part_lse[item_b * splits + split] = l_b > 0.f ? m_b + log2f(l_b) : -INFINITY;
+  }
+}
+
+static int g_latent_sms = 0;
+
+static int latent_sm_count() {
+  if (g_latent_sms == 0) {
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&g_latent_sms, cudaDevAttrMultiProcessorCount, device);
+    if (g_latent_sms <= 0) g_latent_sms = 148;
+  }
+  return g_latent_sms;
+}
+
+template <int DV, int VS, int ROWW>
+static int launch_latent(const __nv_bfloat16* q_full, const __nv_bfloat16* cache, const int* block_tables, int table_stride,
+                         const int* query_start, const int* context_lens, int page_size, int heads, int dk, float scale,
+                         int window, __nv_bfloat16* out, float* part_o, float* part_lse, int splits, int n_requests,
+                         int max_query_len, cudaStream_t stream) {
+  const size_t smem = (size_t)(16 * ROWW + 2 * LBN) * (dk + 8) * sizeof(__nv_bfloat16);
+  static size_t allowed = 0;       // per instantiation
+  if (smem > allowed) {
+    cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<DV, VS, ROWW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) MS_FAIL("latent_attention_mma: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+    allowed = smem;
+  }
+  const long long rows = (long long)max_query_len * heads;
+  dim3 grid((unsigned)((rows + 16 * ROWW - 1) / (16 * ROWW)), n_requests, splits);
+  ms::launch(latent_attention_mma_kernel<DV, VS, ROWW>, grid, 32 * VS * ROWW, smem, stream, q_full, cache, block_tables,
+             table_stride, query_start, context_lens, page_size, heads, dk, scale * 1.4426950408889634f, window, out, part_o,
+             part_lse, splits);
+  MS_CHECK_LAUNCH("latent_attention_mma");
+  return 0;
+}
+
+}  // namespace ms
+
+using namespace ms;
+
+// Sizes the tensor-core kernel takes: a latent of 64, 96, 128, 256 or 512 numbers, a rotated part that is a multiple
+// of 16 (or empty), rows of at most 1024 numbers.
+MS_EXPORT int ms_latent_attention_mma_supports(int rank, int rot, int heads) {
+  const bool rank_ok = rank == 64 || rank == 96 || rank == 128 || rank == 256 || rank == 512;
+  return rank_ok && rot >= 0 && rot % 16 == 0 && rank + rot <= 1024 && heads >= 1 && heads <= 65535 ? 1 : 0;
+}
+
+// How many ranges the keys of a step are cut into: 1 for steps with prompt portions; for steps of single tokens enough
+// that the blocks fill the multiprocessors about twice, at most 16 and at most one range per two key tiles of the longest
+// context (`max_context_len`, an upper bound).
 MS_EXPORT int ms_latent_attention_mma_splits(int rank, int rot, int heads, int n_requests, int max_query_len,
-                                             int max_context_len) { return 1; }
+                                             int max_context_len) {
+  if (max_query_len != 1 || n_requests <= 0) return 1;
+  const int row_tiles = (heads + 15) / 16;
+  const int blocks = n_requests * row_tiles;
+  int splits = (2 * latent_sm_count() + blocks - 1) / blocks;
+  const int by_keys = (max_context_len + 2 * LBN - 1) / (2 * LBN);
+  if (splits > by_keys) splits = by_keys;
+  if (splits > 16) splits = 16;
+  return splits < 1 ? 1 : splits;
+}
 
+// q_full [n_tokens, heads, rank + rot] and out [n_tokens, heads, rank] bfloat16; cache [pages, page_size, rank + rot];
+// part_o float32 [n_tokens * heads * splits, rank] and part_lse [n_tokens * heads * splits] when splits > 1.
 MS_EXPORT int ms_latent_attention_mma(const void* q_full, const void* cache, const int* block_tables, int table_stride,
                                       const int* query_start, const int* context_lens, int page_size, int heads, int rank,
                                       int rot, float scale, int window, void* out, float* part_o, float* part_lse, int splits,
                                       int n_requests, int max_query_len, int n_tokens, cudaStream_t stream) {
-  MS_FAIL("latent_attention_mma: no sizes are supported yet");
+  if (n_tokens == 0 || n_requests == 0) return 0;
+  MS_REQUIRE(ms_latent_attention_mma_supports(rank, rot, heads), "latent_attention_mma: sizes %d + %d are not supported", rank, rot);
+  MS_REQUIRE(page_size > 0 && max_query_len > 0, "latent_attention_mma: page size %d, longest portion %d", page_size, max_query_len);
+  MS_REQUIRE(splits >= 1 && splits <= 16 && (splits == 1 || (part_o && part_lse)), "latent_attention_mma: %d splits", splits);
+  MS_REQUIRE(n_requests <= 65535, "latent_attention_mma: %d requests in one launch is too many", n_requests);
+  const int dk = rank + rot;
+  const bool single = max_query_len == 1;
+  const __nv_bfloat16* q = (const __nv_bfloat16*)q_full;
+  const __nv_bfloat16* c = (const __nv_bfloat16*)cache;
+  __nv_bfloat16* o = (__nv_bfloat16*)out;
+  int code = 0;
+#define MS_LATENT_CASE(DV, VS)                                                                                                  \
+  if (rank == DV) {                                                                                                             \
+    code = single ? launch_latent<DV, VS, 1>(q, c, block_tables, table_stride, query_start, context_lens, page_size, heads, dk, \
+                                             scale, window, o, part_o, part_lse, splits, n_requests, max_query_len, stream)     \
+                  : launch_latent<DV, VS, 4>(q, c, block_tables, table_stride, query_start, context_lens, page_size, heads, dk, \
+                                             scale, window, o, part_o, part_lse, splits, n_requests, max_query_len, stream);    \
+    if (code) return code;                                                                                                      \
+  }
+  MS_LATENT_CASE(64, 1)
+  MS_LATENT_CASE(96, 1)
+  MS_LATENT_CASE(128, 1)
+  MS_LATENT_CASE(256, 2)
+  MS_LATENT_CASE(512, 2)
+#undef MS_LATENT_CASE
+  if (splits > 1) {
+    const int items = n_tokens * heads;
+    if (rank == 64) launch_attention_combine<64>(part_o, part_lse, o, splits, items, stream);
+    else if (rank == 96) launch_attention_combine<96>(part_o, part_lse, o, splits, items, stream);
+    else if (rank == 128) launch_attention_combine<128>(part_o, part_lse, o, splits, items, stream);
+    else if (rank == 256) launch_attention_combine<256>(part_o, part_lse, o, splits, items, stream);
+    else launch_attention_combine<512>(part_o, part_lse, o, splits, items, stream);
+    MS_CHECK_LAUNCH("latent_attention_mma: merge of the key ranges");
+  }
+  return 0;
 }

@@ -94,13 +94,19 @@ def test_latent_prepare(dtype, heads, dim, rot, rank, rot_dims):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,rank,rot,page,window", [(3, 40, 16, 4, None), (1, 22, 6, 8, None), (8, 64, 16, 16, None),
-                                                        (16, 96, 32, 8, 21), (5, 128, 64, 16, None), (2, 9, 0, 4, 7)])
-def test_latent_attention_kernel(dtype, heads, rank, rot, page, window):
-    """Prompt portions beside single tokens over a paged cache of latent rows, against the plain statement."""
+                                                        (16, 96, 32, 8, 21), (5, 128, 64, 16, None), (2, 9, 0, 4, 7),
+                                                        (20, 256, 32, 16, None), (16, 512, 64, 8, 40), (6, 128, 0, 4, None)])
+@pytest.mark.parametrize("single", [False, True])
+def test_latent_attention_kernel(dtype, heads, rank, rot, page, window, single):
+    """Prompt portions beside single tokens (or single tokens only, as a decode step has them: the keys are then cut
+    into ranges that a second kernel merges) over a paged cache of latent rows, against the plain statement.  The sizes
+    cover the tensor-core kernel's (bfloat16; latent 64, 96, 128, 256, 512 with a rotated part that is a multiple of 16)
+    and others, which run the general kernel."""
     from miniserve_b200 import kernels
 
     dk = rank + rot
-    lens, news = [70, 33, 1, 130], [70, 1, 1, 9]              # context lengths and how many of their tokens are new
+    lens = [70, 33, 1, 130]                                   # context lengths, and how many of their tokens are new
+    news = [1, 1, 1, 1] if single else [70, 1, 1, 9]
     pages_of, tables, next_page = [], [], 0
     order = torch.randperm(64, generator=torch.Generator().manual_seed(7)).tolist()
     width = max((l + page - 1) // page for l in lens)
