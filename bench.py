@@ -473,6 +473,169 @@ def sweep_workload(bench: Bench, args) -> int:
     return 0
 
 
+# --------------------------------------------------------------------------- designs side by side (--workload designs)
+
+def _latent(heads, dim, rot, vdim, rank):
+    return dict(heads=heads, dim=dim, rot_dim=rot, vdim=vdim, kv_rank=rank, scale=(dim + rot) ** -0.5,
+                rot=dict(base=10000.0, dims=rot, scaling=dict(factor=4.0, original=4096, fast=32.0, slow=1.0)))
+
+
+def _vesidra(width, layers, mixer, dense_ff, experts, top, expert_ff, shared_ff, vocab):
+    entries = []
+    for index in range(layers):
+        mlp = dict(kind="dense", ff=dense_ff) if index % 2 == 0 else dict(
+            kind="moe", expert=dict(ff=expert_ff), router=dict(experts=experts, top=top), shared=dict(ff=shared_ff))
+        entries.append(dict(type="latent_attention", mixer=mixer, mlp=mlp))
+    return dict(architecture="Vesidra", vocab=vocab, width=width, embedding=dict(scale=float(width) ** 0.5), norm=dict(eps=1e-6),
+                layers=entries)
+
+
+# Layer sizes that resemble real models' (random weights, four layers each: two with a gated MLP, two with experts), and
+# the Qwen3 layers of equal width, head count and inner size beside them.
+DESIGN_SIZES = {
+    # latent 256 + 32, sixteen heads of 64 + 32; 16 experts of 1,024, four per token, and a shared one of 2,048
+    "small": dict(vesidra=_vesidra(2048, 4, _latent(16, 64, 32, 64, 256), 6144, 16, 4, 1024, 2048, 32000),
+                  qwen3=dict(hidden_size=2048, intermediate_size=6144, num_attention_heads=16, num_key_value_heads=8, head_dim=128)),
+    # latent 512 + 64, sixteen heads of 128 + 64; 64 experts of 1,408, six per token, and a shared one of 2,816
+    "lite": dict(vesidra=_vesidra(2048, 4, _latent(16, 128, 64, 128, 512), 10944, 64, 6, 1408, 2816, 32000),
+                 qwen3=dict(hidden_size=2048, intermediate_size=10944, num_attention_heads=16, num_key_value_heads=8, head_dim=128)),
+}
+
+
+def designs_workload(args) -> int:
+    """``--workload designs``: prompt and decode throughput of Vesidra at sizes that resemble real models' layers, beside
+    the Qwen3 decoder at equal width, depth, head count and inner size; one JSON line per size and design, with each
+    step's kernels (device time by kernel, from the framework profiler) so that like kernels can be set side by side."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    import miniserve_b200  # noqa: F401
+    from miniserve_b200.config import EngineConfig
+    from miniserve_b200.engine.runtime import build_runtime
+    from miniserve_b200.engine.step import StepEntry
+
+    peak, peak_source = peaks()
+    batch, context, prompt_tokens, steps, warmup = args.batch, args.context or 2048, PREFILL_TOKENS, args.steps, max(args.warmup, 3)
+    generator = torch.Generator().manual_seed(1)
+    for size_name, pair in DESIGN_SIZES.items():
+        if args.design_size and size_name != args.design_size:
+            continue
+        layers = len(pair["vesidra"]["layers"])
+        vocab = pair["vesidra"]["vocab"]
+        configs = {"vesidra": pair["vesidra"],
+                   "qwen3": dict(MODEL, **pair["qwen3"], num_hidden_layers=layers, vocab_size=vocab, tie_word_embeddings=True)}
+        for design, config in configs.items():
+            pages = batch * ((context + steps + 8 + PAGE_SIZE - 1) // PAGE_SIZE) + prompt_tokens // PAGE_SIZE + 8
+            runtime = build_runtime(None, EngineConfig(
+                dtype="bfloat16", max_model_len=max(context + steps + 8, prompt_tokens), max_num_seqs=batch + 1, kv_block_size=PAGE_SIZE,
+                num_kv_blocks=pages, max_num_batched_tokens=max(8192, prompt_tokens), enable_prefix_cache=False,
+                decode_execution="cuda_graph"), config_dict=config, weights_seed=0)
+            manager, run = runtime.manager, runtime.step_function.run
+            tokens_of = lambda n: torch.randint(0, vocab, (n,), generator=generator).tolist()
+
+            def timed(fn) -> float:
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                start.record()
+                fn()
+                end.record()
+                torch.cuda.synchronize()
+                return start.elapsed_time(end) / 1e3
+
+            def kernels_of(fn) -> list:
+                """[kernel, launches, device microseconds] of one call, largest first (from the profiler's trace file)."""
+                import tempfile
+
+                with profile(activities=[ProfilerActivity.CUDA]) as profiler:
+                    fn()
+                    torch.cuda.synchronize()
+                with tempfile.TemporaryDirectory() as folder:
+                    trace_file = os.path.join(folder, "trace.json")
+                    profiler.export_chrome_trace(trace_file)
+                    with open(trace_file) as handle:
+                        events = [e for e in json.load(handle)["traceEvents"] if e.get("cat") == "kernel"]
+                totals: dict = {}
+                for event in events:
+                    entry = totals.setdefault(event["name"].split("(")[0].replace("void ", "")[:60], [0, 0.0])
+                    entry[0] += 1
+                    entry[1] += event["dur"]
+                return [[name, count, round(us, 1)] for name, (count, us) in sorted(totals.items(), key=lambda kv: -kv[1][1])[:14]]
+
+            prompt = tokens_of(prompt_tokens)
+
+            def prompt_step() -> None:
+                manager.admit("p")
+                reservation = manager.prepare([("p", prompt_tokens)])
+                run([StepEntry("p", prompt, [prompt_tokens - 1])], reservation)
+                manager.commit(reservation)
+                manager.release("p")
+
+            for _ in range(warmup):
+                prompt_step()
+            prompt_seconds = sorted(timed(prompt_step) for _ in range(9))[4]
+            prompt_kernels = kernels_of(prompt_step)
+
+            ids = [f"d{i}" for i in range(batch)]
+            for rid in ids:
+                manager.admit(rid)
+                runtime.storage.reset_slot(manager.requests[rid].slot, 0.0, 1.0, 0, 0)
+                done = 0
+                while done < context:
+                    take = min(2048, context - done)
+                    reservation = manager.prepare([(rid, take)])
+                    run([StepEntry(rid, tokens_of(take), [])], reservation)
+                    manager.commit(reservation)
+                    done += take
+
+            def decode(count: int) -> None:
+                for _ in range(count):
+                    reservation = manager.prepare([(rid, 1) for rid in ids])
+                    run([StepEntry(rid, [1], [0]) for rid in ids], reservation, [0] * batch)
+                    manager.commit(reservation)
+
+            def rewind() -> None:
+                for rid in ids:
+                    manager.truncate(rid, context)
+
+            decode(warmup)
+            rewind()
+            times = []
+            for _ in range(7):
+                times.append(timed(lambda: decode(steps)) / steps)
+                rewind()
+            decode_seconds = sorted(times)[len(times) // 2]
+            decode_kernels = kernels_of(lambda: decode(1))
+            rewind()
+            for rid in ids:
+                manager.release(rid)
+            matrix_bytes = sum(t.numel() * t.element_size() for t in _weights_of(runtime.model))
+            print(json.dumps({
+                "workload": "designs", "size": size_name, "design": design, "dtype": "bf16", "layers": layers,
+                "data": "synthetic (seeded uniform token ids, random weights)",
+                "prefill": {"tokens": prompt_tokens, "ms": round(prompt_seconds * 1e3, 3), "tok_s": round(prompt_tokens / prompt_seconds, 1)},
+                "decode": {"batch": batch, "context": context, "ms_per_step": round(decode_seconds * 1e3, 4),
+                           "tok_s": round(batch / decode_seconds, 1), "execution": "cuda_graph"},
+                "weight_bytes": matrix_bytes,
+                "peak": {"hbm_gbs": peak["hbm_gbs"], "bf16_tflops": peak["bf16_tflops"], "source": peak_source},
+                "prefill_kernels_us": prompt_kernels, "decode_kernels_us": decode_kernels}), flush=True)
+            del runtime, manager, run
+            torch.cuda.empty_cache()
+    return 0
+
+
+def _weights_of(model) -> list:
+    """Every device tensor that the model's parts hold (what a decode step can read at most)."""
+    import torch
+
+    seen, found = set(), []
+    for part in list(model.parts()) + [model]:
+        for value in vars(part).values():
+            if isinstance(value, torch.Tensor) and value.is_cuda and value.data_ptr() not in seen:
+                seen.add(value.data_ptr())
+                found.append(value)
+    return found
+
+
 def main() -> int:
     global CONTEXT, PREFILL_TOKENS
     parser = argparse.ArgumentParser()
@@ -484,7 +647,9 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=None,
                         help="fewer layers than the model has (named in the output); for quick checks only")
     parser.add_argument("--skip-points", action="store_true")
-    parser.add_argument("--workload", choices=("default", "mixed", "sweep"), default="default")
+    parser.add_argument("--workload", choices=("default", "mixed", "sweep", "designs"), default="default",
+                        help="designs: Vesidra beside Qwen3 at equal layer sizes (prompt and decode throughput, kernels by time)")
+    parser.add_argument("--design-size", choices=sorted(DESIGN_SIZES), default=None, help="with --workload designs: one size only")
     parser.add_argument("--sweep-prompt", type=int, default=1024)
     parser.add_argument("--sweep-new", type=int, default=128)
     parser.add_argument("--timeline", metavar="FILE", default=None,
@@ -508,6 +673,8 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.workload == "designs":
+        return designs_workload(args)
 
     shape = dict(MODEL, **SHAPES[args.shape])
     if args.layers is None:

@@ -9,60 +9,83 @@
 //   ms_expert_combine   out[token] = sum over its choices of weight * result row (+ a shared expert's output)
 //   ms_relu_square      x = max(x, 0)^2 in place
 //
-// The products accumulate in float32 with one thread per output element summing k in ascending order, so a row's
-// result does not depend on what else is in the batch or on where the row was sorted to.
+// The products accumulate in float32.  The float32 form has one thread per output element summing k in ascending order;
+// the bfloat16 form runs on the tensor cores.  In both a row's result depends on the row and its expert alone, not on
+// what else is in the batch or on where the row was sorted to.
 #include "common.cuh"
 #include "mma_common.cuh"
 
 namespace ms {
 
-// One warp per token.  logits[e] = sum_c x[c] W[e, c] + b[e] (lane-strided partial sums, then a fixed tree).  The
-// `top` largest are taken one after the other (ties: the lower index); weights are exp(l - l_max) / sum over the taken.
-template <typename T>
-__global__ void router_topk_kernel(const T* __restrict__ x, const float* __restrict__ weight, const float* __restrict__ bias,
-                                   int width, int experts, int top, int* __restrict__ ids, float* __restrict__ weights,
-                                   int n_tokens) {
+// A block of four warps per RT tokens, whose rows wait in shared memory as float32.  Warp w takes the experts w, w + 4,
+// ...: it reads an expert's weight row once and forms the RT tokens' logits beside one another,
+// logits[t][e] = sum_c x_t[c] W[e, c] + b[e] (lane-strided partial sums, then a fixed tree: a token's logits do not
+// depend on its neighbours).  Then warp t takes token t: the `top` largest one after the other (ties: the lower
+// index); weights are exp(l - l_max) / sum over the taken.
+template <typename T, int RT>
+__global__ void __launch_bounds__(128)
+router_topk_kernel(const T* __restrict__ x, const float* __restrict__ weight, const float* __restrict__ bias,
+                   int width, int experts, int top, int* __restrict__ ids, float* __restrict__ weights, int n_tokens) {
   grid_dependency_wait();
   grid_dependency_launch();
   extern __shared__ float smem[];
-  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float* logits = smem + (size_t)warp * (experts + top);
-  float* taken = logits + experts;
-  const int n = blockIdx.x * warps + warp;
-  if (n >= n_tokens) return;
-  const T* row = x + (size_t)n * width;
-  for (int e = 0; e < experts; ++e) {
-    const float* w = weight + (size_t)e * width;
-    float sum = 0.f;
-    for (int c = lane; c < width; c += 32) sum += to_float(row[c]) * w[c];
-    sum = warp_sum(sum);
-    if (lane == 0) logits[e] = sum + (bias ? bias[e] : 0.f);
+  float* xs = smem;                                   // [RT][width]
+  float* all_logits = smem + (size_t)RT * width;      // [RT][experts + top]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * RT;
+  for (int i = threadIdx.x; i < RT * width; i += blockDim.x) {
+    const int t = i / width, c = i % width;
+    xs[i] = n0 + t < n_tokens ? to_float(x[(size_t)(n0 + t) * width + c]) : 0.f;
   }
-  __syncwarp();
-  for (int k = 0; k < top; ++k) {
-    float best = -INFINITY;
-    int best_e = 0x7fffffff;
-    for (int e = lane; e < experts; e += 32) {
-      const float v = logits[e];
-      if (v > best) { best = v; best_e = e; }       // ascending e: the lower index wins a tie
+  __syncthreads();
+  for (int e = warp; e < experts; e += 4) {
+    const float* w = weight + (size_t)e * width;
+    float sum[RT];
+#pragma unroll
+    for (int t = 0; t < RT; ++t) sum[t] = 0.f;
+#pragma unroll 4
+    for (int c = lane; c < width; c += 32) {
+      const float wc = w[c];
+#pragma unroll
+      for (int t = 0; t < RT; ++t) sum[t] += xs[t * width + c] * wc;
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float other = __shfl_xor_sync(0xffffffffu, best, o);
-      const int other_e = __shfl_xor_sync(0xffffffffu, best_e, o);
-      if (other > best || (other == best && other_e < best_e)) { best = other; best_e = other_e; }
+    for (int t = 0; t < RT; ++t) {
+      const float total = warp_sum(sum[t]);
+      if (lane == 0) all_logits[t * (experts + top) + e] = total + (bias ? bias[e] : 0.f);
     }
-    if (lane == 0) {
-      taken[k] = best;
-      ids[(size_t)n * top + k] = best_e;
-      logits[best_e] = -INFINITY;
-    }
-    __syncwarp();
   }
-  const float peak = taken[0];
-  float total = 0.f;
-  for (int k = 0; k < top; ++k) total += expf(taken[k] - peak);
-  for (int k = lane; k < top; k += 32) weights[(size_t)n * top + k] = expf(taken[k] - peak) / total;
+  __syncthreads();
+  for (int t = warp; t < RT; t += 4) {
+    const int n = n0 + t;
+    if (n >= n_tokens) continue;
+    float* logits = all_logits + (size_t)t * (experts + top);
+    float* taken = logits + experts;
+    for (int k = 0; k < top; ++k) {
+      float best = -INFINITY;
+      int best_e = 0x7fffffff;
+      for (int e = lane; e < experts; e += 32) {
+        const float v = logits[e];
+        if (v > best) { best = v; best_e = e; }       // ascending e: the lower index wins a tie
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, best, o);
+        const int other_e = __shfl_xor_sync(0xffffffffu, best_e, o);
+        if (other > best || (other == best && other_e < best_e)) { best = other; best_e = other_e; }
+      }
+      if (lane == 0) {
+        taken[k] = best;
+        ids[(size_t)n * top + k] = best_e;
+        logits[best_e] = -INFINITY;
+      }
+      __syncwarp();
+    }
+    const float peak = taken[0];
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) total += expf(taken[k] - peak);
+    for (int k = lane; k < top; k += 32) weights[(size_t)n * top + k] = expf(taken[k] - peak) / total;
+  }
 }
 
 // One block.  offsets[e] .. offsets[e + 1] is expert e's segment of the sorted order; order[i] is the pair (token * top
@@ -168,6 +191,108 @@ expert_linear_kernel(const T* __restrict__ A, int lda, const int* __restrict__ o
   }
 }
 
+// The same product on the tensor cores (bfloat16, mma.sync.m16n8k16, float32 sums): tiles of 64 rows x 128 columns, k in
+// steps of 32 through three cp.async stages; eight warps, each 32 x 32 of the tile.  Rows of A are gathered through
+// `order` as above (a row's address is looked up once).  Inner size and column count multiples of 8.
+constexpr int GBM = 64, GBN = 128, GBK = 32, GSTAGES = 3, GLD = GBK + 8;
+
+__global__ void __launch_bounds__(256)
+expert_linear_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int* __restrict__ order, int top,
+                         const __nv_bfloat16* __restrict__ W, __nv_bfloat16* __restrict__ C, int ldc,
+                         const int* __restrict__ offsets, int experts, int N, int K, int relu_square) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  __shared__ __align__(16) __nv_bfloat16 As[GSTAGES][GBM][GLD];
+  __shared__ __align__(16) __nv_bfloat16 Bs[GSTAGES][GBN][GLD];
+  __shared__ int src_row[GBM];
+  int tile = blockIdx.y, expert = 0, first = 0, end = 0;
+  for (; expert < experts; ++expert) {
+    first = offsets[expert];
+    end = offsets[expert + 1];
+    const int tiles = (end - first + GBM - 1) / GBM;
+    if (tile < tiles) break;
+    tile -= tiles;
+  }
+  if (expert == experts) return;
+  const int m0 = first + tile * GBM, n0 = blockIdx.x * GBN;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid < GBM) {
+    const int i = m0 + tid;
+    src_row[tid] = i < end ? (order ? order[i] / top : i) : -1;
+  }
+  __syncthreads();
+  const __nv_bfloat16* We = W + (size_t)expert * N * K;
+  const int a_r = tid >> 2, a_c = (tid & 3) * 8;                   // this thread's 16 bytes of the A tile
+  const int a_src = src_row[a_r];
+  auto load_stage = [&](int stage, int k0) {
+    cp_async_16(&As[stage][a_r][a_c], A + (size_t)(a_src < 0 ? 0 : a_src) * lda + k0 + a_c, a_src >= 0 && k0 + a_c < K);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = (tid + i * 256) >> 2;
+      const bool valid = n0 + r < N && k0 + a_c < K;
+      cp_async_16(&Bs[stage][r][a_c], We + (size_t)(valid ? n0 + r : 0) * K + (valid ? k0 + a_c : 0), valid);
+    }
+  };
+  const int k_tiles = (K + GBK - 1) / GBK;
+#pragma unroll
+  for (int s = 0; s < GSTAGES - 1; ++s) {
+    if (s < k_tiles) load_stage(s, s * GBK);
+    cp_async_commit();
+  }
+  const int warp_m = warp >> 2, warp_n = warp & 3;
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+  for (int kt = 0; kt < k_tiles; ++kt) {
+    cp_async_wait<GSTAGES - 2>();
+    __syncthreads();
+    const int next = kt + GSTAGES - 1;
+    if (next < k_tiles) load_stage(next % GSTAGES, next * GBK);
+    cp_async_commit();
+    const int stage = kt % GSTAGES;
+#pragma unroll
+    for (int kk = 0; kk < GBK / 16; ++kk) {
+      unsigned a[2][4], b[2][4];
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi)
+        ldmatrix_x4(a[mi], &As[stage][warp_m * 32 + mi * 16 + (lane & 15)][kk * 16 + (lane >> 4) * 8]);
+#pragma unroll
+      for (int np = 0; np < 2; ++np)
+        ldmatrix_x4(b[np], &Bs[stage][warp_n * 32 + np * 16 + (lane & 7) + (lane >> 4) * 8][kk * 16 + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+        for (int np = 0; np < 2; ++np) {
+          mma_bf16(acc[mi][2 * np], a[mi], b[np][0], b[np][1]);
+          mma_bf16(acc[mi][2 * np + 1], a[mi], b[np][2], b[np][3]);
+        }
+    }
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+    for (int ni = 0; ni < 4; ++ni) {
+      const int n = n0 + warp_n * 32 + ni * 8 + (lane & 3) * 2;
+      if (n >= N) continue;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int m = m0 + warp_m * 32 + mi * 16 + (lane >> 2) + half * 8;
+        if (m >= end) continue;
+        float v0 = acc[mi][ni][2 * half], v1 = acc[mi][ni][2 * half + 1];
+        if (relu_square) {
+          v0 = fmaxf(v0, 0.f);
+          v1 = fmaxf(v1, 0.f);
+          v0 *= v0;
+          v1 *= v1;
+        }
+        *reinterpret_cast<__nv_bfloat162*>(C + (size_t)m * ldc + n) = __floats2bfloat162_rn(v0, v1);
+      }
+    }
+}
+
 // One block per token: out[n, c] = sum_k weights[n, k] * Y[place[n * top + k], c] (+ shared[n, c]), k ascending, float32.
 template <typename T>
 __global__ void expert_combine_kernel(const T* __restrict__ Y, int ldy, const int* __restrict__ place,
@@ -209,11 +334,15 @@ MS_EXPORT int ms_router_topk(const void* x, int dtype, const float* weight, cons
                              int top, int* ids, float* weights, int n_tokens, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   MS_REQUIRE(experts > 0 && top > 0 && top <= experts, "router_topk: %d of %d experts", top, experts);
-  const int warps = 4;
-  const size_t smem = (size_t)warps * (experts + top) * sizeof(float);
-  MS_REQUIRE(smem <= 48 * 1024, "router_topk: %d experts need %zu bytes of shared memory", experts, smem);
-  MS_EXP_DISPATCH(dtype, (ms::launch(router_topk_kernel<T>, (n_tokens + warps - 1) / warps, warps * 32, smem, stream, (const T*)x,
-                                     weight, bias, width, experts, top, ids, weights, n_tokens)));
+  const size_t one = ((size_t)width + experts + top) * sizeof(float);
+  MS_REQUIRE(one <= 48 * 1024, "router_topk: a row of %d numbers and %d experts need %zu bytes of shared memory", width, experts, one);
+  if (4 * one <= 48 * 1024) {
+    MS_EXP_DISPATCH(dtype, (ms::launch(router_topk_kernel<T, 4>, (n_tokens + 3) / 4, 128, 4 * one, stream, (const T*)x, weight, bias,
+                                       width, experts, top, ids, weights, n_tokens)));
+  } else {
+    MS_EXP_DISPATCH(dtype, (ms::launch(router_topk_kernel<T, 1>, n_tokens, 128, one, stream, (const T*)x, weight, bias, width,
+                                       experts, top, ids, weights, n_tokens)));
+  }
   MS_CHECK_LAUNCH("router_topk");
   return 0;
 }
@@ -234,6 +363,14 @@ MS_EXPORT int ms_expert_linear(const void* A, int dtype, int lda, const int* ord
   MS_REQUIRE(K > 0 && top > 0, "expert_linear: inner size %d and choices %d must be positive", K, top);
   const int row_tiles = (pairs + EBM - 1) / EBM + experts;      // every segment may end in a partial tile
   MS_REQUIRE(row_tiles <= 65535, "expert_linear: %d rows in one launch is too many", pairs);
+  if (dtype == MS_BF16 && K % 8 == 0 && N % 8 == 0 && lda % 8 == 0 && ldc % 2 == 0) {
+    static_assert(GBM == EBM, "the two kernels walk the same row tiles");
+    dim3 mma_grid((N + GBN - 1) / GBN, row_tiles);
+    ms::launch(expert_linear_mma_kernel, mma_grid, 256, 0, stream, (const __nv_bfloat16*)A, lda, order, top,
+               (const __nv_bfloat16*)W, (__nv_bfloat16*)C, ldc, offsets, experts, N, K, relu_square);
+    MS_CHECK_LAUNCH("expert_linear (tensor cores)");
+    return 0;
+  }
   dim3 grid((N + EBN - 1) / EBN, row_tiles);
   MS_EXP_DISPATCH(dtype, (ms::launch(expert_linear_kernel<T>, grid, 256, 0, stream, (const T*)A, lda, order, top, (const T*)W,
                                      (T*)C, ldc, offsets, experts, N, K, relu_square)));
