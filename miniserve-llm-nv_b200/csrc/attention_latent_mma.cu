@@ -60,16 +60,18 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_full, const __nv
   const int t_end = min(tile_end, t_begin + per_split);
 
   const int chunks = dk >> 3;           // 16-byte pieces per row
+  // A key row of a tile belongs to THREADS / 32 threads, which look its page up once and then request its pieces one
+  // after the other (a lookup per piece would put a trip to the L2 cache before every request).
+  constexpr int TPR = THREADS / LBN;
+  static_assert(THREADS % LBN == 0 && TPR >= 1, "whole threads per key row");
+  const int load_r = tid / TPR, load_c = tid % TPR;
   auto load_keys = [&](int tile, int buffer) {
-    __nv_bfloat16* dst = k_s + (size_t)buffer * LBN * dkp;
-    for (int i = tid; i < LBN * chunks; i += THREADS) {
-      const int r = i / chunks, c = i % chunks;
-      const int key = tile * LBN + r;
-      const bool valid = key <= pos_last;
-      const int page = valid ? table[key / page_size] : 0;
-      const __nv_bfloat16* src = cache + ((size_t)page * page_size + (valid ? key % page_size : 0)) * dk + c * 8;
-      cp_async_16(dst + r * dkp + c * 8, src, valid);
-    }
+    const int key = tile * LBN + load_r;
+    const bool valid = key <= pos_last;
+    const int page = valid ? table[key / page_size] : 0;
+    const __nv_bfloat16* src = cache + ((size_t)page * page_size + (valid ? key % page_size : 0)) * dk;
+    __nv_bfloat16* dst = k_s + ((size_t)buffer * LBN + load_r) * dkp;
+    for (int c = load_c; c < chunks; c += TPR) cp_async_16(dst + c * 8, src + c * 8, valid);
   };
   if (t_begin < t_end) {
     const __nv_bfloat16* q_rows = q_full + ((size_t)q0 * heads + m0) * dk;

@@ -1,7 +1,8 @@
 // A feed-forward of routed experts, on the device from the router to the weighted sum, so that a step never waits
 // for the host to learn which experts were chosen (and a captured decode step can hold it):
 //
-//   ms_router_topk      float32 router logits W x + b of every token, the `top` largest, softmax over those alone
+//   ms_router_topk      float32 router logits W x + b of every token (one kernel), the `top` largest and the softmax
+//                       over those alone (a second)
 //   ms_expert_route     sorts the (token, choice) pairs by expert: segment offsets, the pairs in sorted order and
 //                       each pair's place in that order
 //   ms_expert_linear    one product per expert over its segment of rows (rows gathered from the tokens for the first
@@ -17,75 +18,109 @@
 
 namespace ms {
 
-// A block of four warps per RT tokens, whose rows wait in shared memory as float32.  Warp w takes the experts w, w + 4,
-// ...: it reads an expert's weight row once and forms the RT tokens' logits beside one another,
-// logits[t][e] = sum_c x_t[c] W[e, c] + b[e] (lane-strided partial sums, then a fixed tree: a token's logits do not
-// depend on its neighbours).  Then warp t takes token t: the `top` largest one after the other (ties: the lower
-// index); weights are exp(l - l_max) / sum over the taken.
+// Router logits, float32: logits[n][e] = sum_c x_n[c] W[e, c] + b[e].  A block of eight warps holds the rows of RT
+// tokens in shared memory (in their stored type: the conversion is exact) and takes `per_block` experts, warp w the
+// experts w, w + 8, ... of them: it reads an expert's weight row once, sixteen bytes per lane and two such loads
+// ahead of the sums, and forms the RT tokens' logits beside one another.  A logit is the fixed tree over the lanes'
+// sums of their own pieces in ascending order, so it does not depend on the token's neighbours or on the grid.
 template <typename T, int RT>
-__global__ void __launch_bounds__(128)
-router_topk_kernel(const T* __restrict__ x, const float* __restrict__ weight, const float* __restrict__ bias,
-                   int width, int experts, int top, int* __restrict__ ids, float* __restrict__ weights, int n_tokens) {
+__global__ void __launch_bounds__(256)
+router_logits_kernel(const T* __restrict__ x, const float* __restrict__ weight, const float* __restrict__ bias,
+                     int width, int experts, int per_block, float* __restrict__ logits, int n_tokens) {
   grid_dependency_wait();
   grid_dependency_launch();
-  extern __shared__ float smem[];
-  float* xs = smem;                                   // [RT][width]
-  float* all_logits = smem + (size_t)RT * width;      // [RT][experts + top]
+  extern __shared__ __align__(16) unsigned char router_smem[];
+  T* xs = reinterpret_cast<T*>(router_smem);          // [RT][width]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * RT;
   for (int i = threadIdx.x; i < RT * width; i += blockDim.x) {
     const int t = i / width, c = i % width;
-    xs[i] = n0 + t < n_tokens ? to_float(x[(size_t)(n0 + t) * width + c]) : 0.f;
+    xs[i] = n0 + t < n_tokens ? x[(size_t)(n0 + t) * width + c] : from_float<T>(0.f);
   }
   __syncthreads();
-  for (int e = warp; e < experts; e += 4) {
+  const int e_end = min(experts, (blockIdx.y + 1) * per_block);
+  for (int e = blockIdx.y * per_block + warp; e < e_end; e += 8) {
     const float* w = weight + (size_t)e * width;
     float sum[RT];
 #pragma unroll
     for (int t = 0; t < RT; ++t) sum[t] = 0.f;
-#pragma unroll 4
-    for (int c = lane; c < width; c += 32) {
-      const float wc = w[c];
+    if ((width & 3) == 0) {
+      for (int c = lane * 4; c < width; c += 256) {
+        const float4 w0 = *reinterpret_cast<const float4*>(w + c);
+        const bool more = c + 128 < width;
+        const float4 w1 = more ? *reinterpret_cast<const float4*>(w + c + 128) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for (int t = 0; t < RT; ++t) sum[t] += xs[t * width + c] * wc;
+        for (int t = 0; t < RT; ++t) {
+          const T* row = xs + t * width + c;
+          sum[t] += to_float(row[0]) * w0.x;
+          sum[t] += to_float(row[1]) * w0.y;
+          sum[t] += to_float(row[2]) * w0.z;
+          sum[t] += to_float(row[3]) * w0.w;
+        }
+        if (more) {
+#pragma unroll
+          for (int t = 0; t < RT; ++t) {
+            const T* row = xs + t * width + c + 128;
+            sum[t] += to_float(row[0]) * w1.x;
+            sum[t] += to_float(row[1]) * w1.y;
+            sum[t] += to_float(row[2]) * w1.z;
+            sum[t] += to_float(row[3]) * w1.w;
+          }
+        }
+      }
+    } else {
+      for (int c = lane; c < width; c += 32) {
+        const float wc = w[c];
+#pragma unroll
+        for (int t = 0; t < RT; ++t) sum[t] += to_float(xs[t * width + c]) * wc;
+      }
     }
 #pragma unroll
     for (int t = 0; t < RT; ++t) {
       const float total = warp_sum(sum[t]);
-      if (lane == 0) all_logits[t * (experts + top) + e] = total + (bias ? bias[e] : 0.f);
+      if (lane == 0 && n0 + t < n_tokens) logits[(size_t)(n0 + t) * experts + e] = total + (bias ? bias[e] : 0.f);
     }
   }
-  __syncthreads();
-  for (int t = warp; t < RT; t += 4) {
-    const int n = n0 + t;
-    if (n >= n_tokens) continue;
-    float* logits = all_logits + (size_t)t * (experts + top);
-    float* taken = logits + experts;
-    for (int k = 0; k < top; ++k) {
-      float best = -INFINITY;
-      int best_e = 0x7fffffff;
-      for (int e = lane; e < experts; e += 32) {
-        const float v = logits[e];
-        if (v > best) { best = v; best_e = e; }       // ascending e: the lower index wins a tie
-      }
+}
+
+// One warp per token: the `top` largest of its logits one after the other (ties: the lower index); weights are
+// exp(l - l_max) / sum over the taken.
+__global__ void router_select_kernel(const float* __restrict__ all_logits, int experts, int top, int* __restrict__ ids,
+                                     float* __restrict__ weights, int n_tokens) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  extern __shared__ float select_smem[];
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* logits = select_smem + (size_t)warp * (experts + top);
+  float* taken = logits + experts;
+  const int n = blockIdx.x * warps + warp;
+  if (n >= n_tokens) return;
+  for (int e = lane; e < experts; e += 32) logits[e] = all_logits[(size_t)n * experts + e];
+  __syncwarp();
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = logits[e];
+      if (v > best) { best = v; best_e = e; }       // ascending e: the lower index wins a tie
+    }
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        const float other = __shfl_xor_sync(0xffffffffu, best, o);
-        const int other_e = __shfl_xor_sync(0xffffffffu, best_e, o);
-        if (other > best || (other == best && other_e < best_e)) { best = other; best_e = other_e; }
-      }
-      if (lane == 0) {
-        taken[k] = best;
-        ids[(size_t)n * top + k] = best_e;
-        logits[best_e] = -INFINITY;
-      }
-      __syncwarp();
+    for (int o = 16; o > 0; o >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, o);
+      const int other_e = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (other > best || (other == best && other_e < best_e)) { best = other; best_e = other_e; }
     }
-    const float peak = taken[0];
-    float total = 0.f;
-    for (int k = 0; k < top; ++k) total += expf(taken[k] - peak);
-    for (int k = lane; k < top; k += 32) weights[(size_t)n * top + k] = expf(taken[k] - peak) / total;
+    if (lane == 0) {
+      taken[k] = best;
+      ids[(size_t)n * top + k] = best_e;
+      logits[best_e] = -INFINITY;
+    }
+    __syncwarp();
   }
+  const float peak = taken[0];
+  float total = 0.f;
+  for (int k = 0; k < top; ++k) total += expf(taken[k] - peak);
+  for (int k = lane; k < top; k += 32) weights[(size_t)n * top + k] = expf(taken[k] - peak) / total;
 }
 
 // One block.  offsets[e] .. offsets[e + 1] is expert e's segment of the sorted order; order[i] is the pair (token * top
@@ -330,20 +365,35 @@ using namespace ms;
 
 // x [n_tokens, width]; weight float32 [experts, width]; bias float32 [experts] or null; ids int32 and weights float32
 // [n_tokens, top].
+// x [n_tokens, width]; weight float32 [experts, width]; bias float32 [experts] or null; logits float32 [n_tokens, experts]
+// (scratch, left holding the logits); ids int32 and weights float32 [n_tokens, top].
 MS_EXPORT int ms_router_topk(const void* x, int dtype, const float* weight, const float* bias, int width, int experts,
-                             int top, int* ids, float* weights, int n_tokens, cudaStream_t stream) {
+                             int top, float* logits, int* ids, float* weights, int n_tokens, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   MS_REQUIRE(experts > 0 && top > 0 && top <= experts, "router_topk: %d of %d experts", top, experts);
-  const size_t one = ((size_t)width + experts + top) * sizeof(float);
-  MS_REQUIRE(one <= 48 * 1024, "router_topk: a row of %d numbers and %d experts need %zu bytes of shared memory", width, experts, one);
-  if (4 * one <= 48 * 1024) {
-    MS_EXP_DISPATCH(dtype, (ms::launch(router_topk_kernel<T, 4>, (n_tokens + 3) / 4, 128, 4 * one, stream, (const T*)x, weight, bias,
-                                       width, experts, top, ids, weights, n_tokens)));
-  } else {
-    MS_EXP_DISPATCH(dtype, (ms::launch(router_topk_kernel<T, 1>, n_tokens, 128, one, stream, (const T*)x, weight, bias, width,
-                                       experts, top, ids, weights, n_tokens)));
-  }
-  MS_CHECK_LAUNCH("router_topk");
+  MS_REQUIRE(dtype == MS_F32 || dtype == MS_BF16, "router_topk: unknown element type code %d", dtype);
+  const size_t element = dtype == MS_F32 ? 4 : 2;
+  MS_REQUIRE((size_t)width * element <= 48 * 1024, "router_topk: a row of %d numbers does not fit the shared memory", width);
+  int rt = 8;                              // tokens per block: as many rows as 32 KB hold, at most eight
+  while (rt > 1 && (size_t)rt * width * element > 32 * 1024) rt >>= 1;
+  const int token_tiles = (n_tokens + rt - 1) / rt;
+  // few token tiles (decode steps): the experts are spread over blocks too, one per warp, so that every weight row has a warp of its own
+  const int per_block = token_tiles >= 128 ? experts : 8;
+  dim3 grid(token_tiles, (experts + per_block - 1) / per_block);
+  const size_t smem = (size_t)rt * width * element;
+#define MS_ROUTER_LOGITS(RT)                                                                                                \
+  MS_EXP_DISPATCH(dtype, (ms::launch(router_logits_kernel<T, RT>, grid, 256, smem, stream, (const T*)x, weight, bias, width, \
+                                     experts, per_block, logits, n_tokens)))
+  if (rt == 8) { MS_ROUTER_LOGITS(8); } else if (rt == 4) { MS_ROUTER_LOGITS(4); } else if (rt == 2) { MS_ROUTER_LOGITS(2); }
+  else { MS_ROUTER_LOGITS(1); }
+#undef MS_ROUTER_LOGITS
+  MS_CHECK_LAUNCH("router_topk: logits");
+  const int warps = 4;
+  const size_t select_smem = (size_t)warps * (experts + top) * sizeof(float);
+  MS_REQUIRE(select_smem <= 48 * 1024, "router_topk: %d experts need %zu bytes of shared memory", experts, select_smem);
+  ms::launch(router_select_kernel, (n_tokens + warps - 1) / warps, warps * 32, select_smem, stream, (const float*)logits, experts,
+             top, ids, weights, n_tokens);
+  MS_CHECK_LAUNCH("router_topk: selection");
   return 0;
 }
 

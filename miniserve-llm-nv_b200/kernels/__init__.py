@@ -16,7 +16,7 @@ import torch
 
 from . import build
 
-ABI_VERSION = 6
+ABI_VERSION = 7
 log = logging.getLogger("miniserve_b200")
 _library: Optional[ctypes.CDLL] = None
 
@@ -507,12 +507,16 @@ def linear_batched(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> 
 
 
 def router_topk(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], top: int, ids: torch.Tensor,
-                weights: torch.Tensor) -> None:
+                weights: torch.Tensor, logits: Optional[torch.Tensor] = None) -> None:
     """Router of a mixture of experts: float32 logits ``x @ weight^T + bias`` (``weight`` float32 ``[E, width]``), the
     ``top`` experts with the largest logits into ``ids`` int32 ``[N, top]`` (ties: the lower index) and the softmax over
-    those logits alone into ``weights`` float32 ``[N, top]``."""
+    those logits alone into ``weights`` float32 ``[N, top]``.  ``logits`` float32 ``[N, E]``: scratch that is left holding
+    the logits (allocated here if not given)."""
     n, width = x.shape
     experts = weight.shape[0]
+    if logits is None:
+        logits = torch.empty((n, experts), dtype=torch.float32, device=x.device)
+    _want(logits, "logits", torch.float32, (n, experts))
     _want(x, "x")
     _want(weight, "weight", torch.float32, (experts, width))
     if bias is not None:
@@ -520,7 +524,7 @@ def router_topk(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     _want(ids, "ids", torch.int32, (n, top))
     _want(weights, "weights", torch.float32, (n, top))
     _check(library().ms_router_topk(_ptr(x), _i(_code(x.dtype)), _ptr(weight), _ptr(bias), _i(width), _i(experts), _i(top),
-                                    _ptr(ids), _ptr(weights), _i(n), _stream()))
+                                    _ptr(logits), _ptr(ids), _ptr(weights), _i(n), _stream()))
 
 
 def expert_route(ids: torch.Tensor, experts: int, offsets: torch.Tensor, order: torch.Tensor, place: torch.Tensor) -> None:

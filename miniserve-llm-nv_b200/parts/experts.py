@@ -78,7 +78,8 @@ class RoutedExperts(Part):
         pairs = n * top
         ids = ctx.buffer("experts.ids", (n, top), torch.int32)
         weights = ctx.buffer("experts.weights", (n, top), torch.float32)
-        kernels.router_topk(x, self.router_weight, self.router_b, top, ids, weights)
+        logits = ctx.buffer("experts.logits", (n, self.experts), torch.float32)
+        kernels.router_topk(x, self.router_weight, self.router_b, top, ids, weights, logits)
         offsets = ctx.buffer("experts.offsets", (self.experts + 1,), torch.int32)
         order = ctx.buffer("experts.order", (pairs,), torch.int32)
         place = ctx.buffer("experts.place", (pairs,), torch.int32)

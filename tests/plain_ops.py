@@ -246,10 +246,12 @@ def linear_batched(x, weight, out):
 # --------------------------------------------------------------------------- routed experts
 
 
-def router_topk(x, weight, bias, top, ids, weights):
+def router_topk(x, weight, bias, top, ids, weights, scratch=None):
     logits = x.double() @ weight.double().T
     if bias is not None:
         logits = logits + bias.double()
+    if scratch is not None:
+        scratch.copy_(logits.to(scratch.dtype))
     ranked = logits.sort(dim=1, descending=True, stable=True)
     ids.copy_(ranked.indices[:, :top].to(ids.dtype))
     weights.copy_(torch.softmax(ranked.values[:, :top], dim=1).to(weights.dtype))
