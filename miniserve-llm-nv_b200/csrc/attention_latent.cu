@@ -14,7 +14,7 @@
 namespace ms {
 
 constexpr int kLatWarps = 4;
-constexpr int kLatMaxLanes = 16;   // value lanes per thread: R up to 512
+constexpr int kLatMaxLanes = 32;   // value lanes per thread: R up to 1024
 
 // Rotation of element c of a vector of `rot` entries whose first `dims` are rotated: entry j < dims / 2 is paired
 // with entry j + dims / 2; the table holds (cos, sin) of the token for each pair (already times the magnitude).

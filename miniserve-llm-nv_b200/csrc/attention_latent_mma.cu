@@ -9,8 +9,10 @@
 //
 // A block owns 16 * ROWW query rows of one request.  Each group of 16 rows has VS warps that share the rows and split the
 // D_V value columns between them (each computes the scores of the whole key tile itself; with D_V = 512 one warp's
-// share of the output, 16 x 512 float32, would not fit its registers).  Key tiles of 32 rows go through two buffers
-// filled by cp.async, the next on its way while this one is multiplied.  Shared-memory rows are D_K + 8 elements
+// share of the output, 16 x 512 float32, would not fit its registers).  Key tiles of 32 rows go through NBUF buffers
+// filled by cp.async, NBUF - 1 tiles on their way while one is multiplied (two buffers for prompt portions, whose
+// blocks of 64 rows leave room for no more with long rows; four for steps of single tokens, where a block walks few
+// tiles and what it waits for is the memory's latency).  Shared-memory rows are D_K + 8 elements
 // apart, which puts the eight rows of an ldmatrix into eight different bank groups for every D_K that is a multiple
 // of 16.
 //
@@ -24,7 +26,7 @@ namespace ms {
 
 constexpr int LBN = 32;       // keys per tile
 
-template <int DV, int VS, int ROWW>
+template <int DV, int VS, int ROWW, int NBUF>
 __global__ void __launch_bounds__(32 * VS * ROWW)
 latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_full, const __nv_bfloat16* __restrict__ cache,
                             const int* __restrict__ block_tables, int table_stride, const int* __restrict__ query_start,
@@ -39,7 +41,7 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_full, const __nv
   grid_dependency_launch();
   const int dkp = dk + 8;
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(latent_smem);     // [16 * ROWW][dkp]
-  __nv_bfloat16* k_s = q_s + 16 * ROWW * dkp;                             // [2][LBN][dkp]
+  __nv_bfloat16* k_s = q_s + 16 * ROWW * dkp;                             // [NBUF][LBN][dkp]
   const int req = blockIdx.y, split = blockIdx.z;
   const int q0 = query_start[req], q_len = query_start[req + 1] - q0, ctx = context_lens[req];
   const int rows = q_len * heads;
@@ -82,6 +84,11 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_full, const __nv
     load_keys(t_begin, 0);
   }
   cp_async_commit();
+#pragma unroll
+  for (int ahead = 1; ahead < NBUF - 1; ++ahead) {
+    if (t_begin + ahead < t_end) load_keys(t_begin + ahead, ahead);
+    cp_async_commit();
+  }
 
   // this thread's two rows of the 16: lane / 4 and lane / 4 + 8
   const int row_a = m0 + wr * 16 + (lane >> 2), row_b = row_a + 8;
@@ -94,11 +101,11 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_full, const __nv
   for (int i = 0; i < DVW / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
   for (int tile = t_begin; tile < t_end; ++tile) {
-    const int buffer = (tile - t_begin) & 1;
-    if (tile + 1 < t_end) load_keys(tile + 1, buffer ^ 1);
+    const int buffer = (tile - t_begin) % NBUF;
+    cp_async_wait<NBUF - 2>();
+    __syncthreads();      // this tile has arrived for everyone, and everyone is done with the tile before it,
+    if (tile + NBUF - 1 < t_end) load_keys(tile + NBUF - 1, (tile - t_begin + NBUF - 1) % NBUF);      // whose buffer is refilled
     cp_async_commit();
-    cp_async_wait<1>();
-    __syncthreads();
     const __nv_bfloat16* kt = k_s + (size_t)buffer * LBN * dkp;
 
     float s[LBN / 8][4];
@@ -168,7 +175,6 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_full, const __nv
         mma_bf16(o[2 * np + 1], p[kk], b[2], b[3]);
       }
     }
-    __syncthreads();        // the buffer is refilled by the loads of the next iteration
   }
   cp_async_wait<0>();
 
@@ -217,22 +223,22 @@ static int latent_sm_count() {
   return g_latent_sms;
 }
 
-template <int DV, int VS, int ROWW>
+template <int DV, int VS, int ROWW, int NBUF>
 static int launch_latent(const __nv_bfloat16* q_full, const __nv_bfloat16* cache, const int* block_tables, int table_stride,
                          const int* query_start, const int* context_lens, int page_size, int heads, int dk, float scale,
                          int window, __nv_bfloat16* out, float* part_o, float* part_lse, int splits, int n_requests,
                          int max_query_len, cudaStream_t stream) {
-  const size_t smem = (size_t)(16 * ROWW + 2 * LBN) * (dk + 8) * sizeof(__nv_bfloat16);
+  const size_t smem = (size_t)(16 * ROWW + NBUF * LBN) * (dk + 8) * sizeof(__nv_bfloat16);
   static size_t allowed = 0;       // per instantiation
   if (smem > allowed) {
-    cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<DV, VS, ROWW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<DV, VS, ROWW, NBUF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) MS_FAIL("latent_attention_mma: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
     allowed = smem;
   }
   const long long rows = (long long)max_query_len * heads;
   dim3 grid((unsigned)((rows + 16 * ROWW - 1) / (16 * ROWW)), n_requests, splits);
-  ms::launch(latent_attention_mma_kernel<DV, VS, ROWW>, grid, 32 * VS * ROWW, smem, stream, q_full, cache, block_tables,
+  ms::launch(latent_attention_mma_kernel<DV, VS, ROWW, NBUF>, grid, 32 * VS * ROWW, smem, stream, q_full, cache, block_tables,
              table_stride, query_start, context_lens, page_size, heads, dk, scale * 1.4426950408889634f, window, out, part_o,
              part_lse, splits);
   MS_CHECK_LAUNCH("latent_attention_mma");
@@ -284,9 +290,9 @@ MS_EXPORT int ms_latent_attention_mma(const void* q_full, const void* cache, con
   int code = 0;
 #define MS_LATENT_CASE(DV, VS)                                                                                                  \
   if (rank == DV) {                                                                                                             \
-    code = single ? launch_latent<DV, VS, 1>(q, c, block_tables, table_stride, query_start, context_lens, page_size, heads, dk, \
+    code = single ? launch_latent<DV, VS, 1, 4>(q, c, block_tables, table_stride, query_start, context_lens, page_size, heads, dk, \
                                              scale, window, o, part_o, part_lse, splits, n_requests, max_query_len, stream)     \
-                  : launch_latent<DV, VS, 4>(q, c, block_tables, table_stride, query_start, context_lens, page_size, heads, dk, \
+                  : launch_latent<DV, VS, 4, 2>(q, c, block_tables, table_stride, query_start, context_lens, page_size, heads, dk, \
                                              scale, window, o, part_o, part_lse, splits, n_requests, max_query_len, stream);    \
     if (code) return code;                                                                                                      \
   }

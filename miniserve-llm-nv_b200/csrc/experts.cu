@@ -33,9 +33,20 @@ router_logits_kernel(const T* __restrict__ x, const float* __restrict__ weight, 
   T* xs = reinterpret_cast<T*>(router_smem);          // [RT][width]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * RT;
-  for (int i = threadIdx.x; i < RT * width; i += blockDim.x) {
-    const int t = i / width, c = i % width;
-    xs[i] = n0 + t < n_tokens ? x[(size_t)(n0 + t) * width + c] : from_float<T>(0.f);
+  constexpr int VEC = 16 / sizeof(T);                 // elements per 16-byte load
+  if (width % VEC == 0) {
+    const int per_row = width / VEC;
+#pragma unroll 4
+    for (int i = threadIdx.x; i < RT * per_row; i += blockDim.x) {
+      const int t = i / per_row, c = (i % per_row) * VEC;
+      const uint4 v = n0 + t < n_tokens ? *reinterpret_cast<const uint4*>(x + (size_t)(n0 + t) * width + c) : make_uint4(0u, 0u, 0u, 0u);
+      *reinterpret_cast<uint4*>(xs + t * width + c) = v;
+    }
+  } else {
+    for (int i = threadIdx.x; i < RT * width; i += blockDim.x) {
+      const int t = i / width, c = i % width;
+      xs[i] = n0 + t < n_tokens ? x[(size_t)(n0 + t) * width + c] : from_float<T>(0.f);
+    }
   }
   __syncthreads();
   const int e_end = min(experts, (blockIdx.y + 1) * per_block);

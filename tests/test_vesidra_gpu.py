@@ -404,7 +404,7 @@ LENGTHS = (1, 7, 8, 9, 16, 17, 33, 64, 65, 150, 301)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,page_size", [("a", 8), ("b", 16), ("c", 16)])
+@pytest.mark.parametrize("name,page_size", [("a", 8), ("b", 16), ("c", 16), ("d", 4)])
 @pytest.mark.parametrize("cutting", list(CUTTINGS))
 def test_cuttings_against_plain(tmp_path, request, dtype, name, page_size, cutting):
     """Whole prompts; last tokens decoded one by one; portions down to two tokens; unequal requests batched together in a

@@ -46,7 +46,12 @@ VESIDRA_C = dict(architecture="Vesidra", vocab=300, width=128, embedding=dict(sc
     layer(mixer(16, 16, 32, 24, 96, 0.2, rot(32, 10000.0, YARN_B)), dict(kind="dense", ff=192)),
     layer(mixer(4, 64, 64, 64, 128, 0.1, rot(64, 500000.0, None)), moe(4, 1, 48, None)),
 ])
-CONFIGS = {"a": VESIDRA_A, "b": VESIDRA_B, "c": VESIDRA_C}
+# A width that is no multiple of eight (rows that start off 16-byte boundaries), tiny heads, two rotated entries.
+VESIDRA_D = dict(architecture="Vesidra", vocab=97, width=100, embedding=dict(scale=10.0), norm=dict(eps=1e-6), layers=[
+    layer(mixer(3, 10, 4, 6, 14, 0.27, rot(2, 50.0, dict(factor=2.0, original=16, fast=2.0, slow=1.0))), moe(4, 2, 10, 6)),
+    layer(mixer(2, 7, 3, 5, 11, 0.31, rot(2, 10000.0, None)), dict(kind="dense", ff=50)),
+])
+CONFIGS = {"a": VESIDRA_A, "b": VESIDRA_B, "c": VESIDRA_C, "d": VESIDRA_D}
 
 
 def steer_routers(tensors: dict, config: dict) -> None:
