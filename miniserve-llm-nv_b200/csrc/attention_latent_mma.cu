@@ -111,6 +111,7 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q_full, const __nv
     float s[LBN / 8][4];
 #pragma unroll
     for (int i = 0; i < LBN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll 2
     for (int kc = 0; kc < (dk >> 4); ++kc) {
       unsigned a[4];
       ldmatrix_x4(a, q_s + (wr * 16 + (lane & 15)) * dkp + kc * 16 + (lane >> 4) * 8);
@@ -288,19 +289,22 @@ MS_EXPORT int ms_latent_attention_mma(const void* q_full, const void* cache, con
   const __nv_bfloat16* c = (const __nv_bfloat16*)cache;
   __nv_bfloat16* o = (__nv_bfloat16*)out;
   int code = 0;
-#define MS_LATENT_CASE(DV, VS)                                                                                                  \
-  if (rank == DV) {                                                                                                             \
-    code = single ? launch_latent<DV, VS, 1, 4>(q, c, block_tables, table_stride, query_start, context_lens, page_size, heads, dk, \
-                                             scale, window, o, part_o, part_lse, splits, n_requests, max_query_len, stream)     \
-                  : launch_latent<DV, VS, 4, 2>(q, c, block_tables, table_stride, query_start, context_lens, page_size, heads, dk, \
-                                             scale, window, o, part_o, part_lse, splits, n_requests, max_query_len, stream);    \
-    if (code) return code;                                                                                                      \
+  // (VS_ONE, VS_MANY: warps per row group in steps of single tokens and in steps with prompt portions.  A latent of 256
+  // has a warp pair per row group in decode steps, where more warps hide more latency, and one warp in prompt steps,
+  // where a pair would compute every score twice.)
+#define MS_LATENT_CASE(DV, VS_ONE, VS_MANY)                                                                                          \
+  if (rank == DV) {                                                                                                                  \
+    code = single ? launch_latent<DV, VS_ONE, 1, 4>(q, c, block_tables, table_stride, query_start, context_lens, page_size, heads, dk, \
+                                                    scale, window, o, part_o, part_lse, splits, n_requests, max_query_len, stream)   \
+                  : launch_latent<DV, VS_MANY, 4, 2>(q, c, block_tables, table_stride, query_start, context_lens, page_size, heads,  \
+                                                     dk, scale, window, o, part_o, part_lse, splits, n_requests, max_query_len, stream); \
+    if (code) return code;                                                                                                           \
   }
-  MS_LATENT_CASE(64, 1)
-  MS_LATENT_CASE(96, 1)
-  MS_LATENT_CASE(128, 1)
-  MS_LATENT_CASE(256, 2)
-  MS_LATENT_CASE(512, 2)
+  MS_LATENT_CASE(64, 1, 1)
+  MS_LATENT_CASE(96, 1, 1)
+  MS_LATENT_CASE(128, 1, 1)
+  MS_LATENT_CASE(256, 2, 1)
+  MS_LATENT_CASE(512, 2, 2)
 #undef MS_LATENT_CASE
   if (splits > 1) {
     const int items = n_tokens * heads;
