@@ -7,18 +7,16 @@
 // transposed by ldmatrix for P V).  The causal mask follows the row's token: row r sees keys up to
 // context - tokens + r / H.
 //
-// A block owns 16 * ROWW query rows of one request.  Each group of 16 rows has VS warps that share the rows and split the
-// D_V value columns between them (each computes the scores of the whole key tile itself; with D_V = 512 one warp's
-// share of the output, 16 x 512 float32, would not fit its registers).  Key tiles of 32 rows go through NBUF buffers
-// filled by cp.async, NBUF - 1 tiles on their way while one is multiplied (two buffers for prompt portions, whose
-// blocks of 64 rows leave room for no more with long rows; four for steps of single tokens, where a block walks few
-// tiles and what it waits for is the memory's latency).  Shared-memory rows are D_K + 8 elements
-// apart, which puts the eight rows of an ldmatrix into eight different bank groups for every D_K that is a multiple
-// of 16.
-//
-// Prompt portions run this kernel with ROWW = 4 and all keys in one block.  Steps of single tokens (H rows per request:
-// one tile of 16 for up to 16 heads) run latent_decode_mma_kernel below, with the keys cut into `splits` ranges over
+// Two kernels.  latent_attention_mma_kernel, for steps with prompt portions: a block owns 16 * ROWW query rows of one
+// request (ROWW = 4 in use) and walks all their keys.  Each group of 16 rows has VS warps that share the rows and split
+// the D_V value columns between them (each computes the scores of the whole key tile itself; VS = 2 only with D_V = 512,
+// where one warp's share of the output, 16 x 512 float32, would not fit its registers).  Key tiles of 32 rows go
+// through NBUF buffers filled by cp.async, NBUF - 1 tiles on their way while one is multiplied (two in use: blocks of
+// 64 rows leave room for no more when rows are long).  latent_decode_mma_kernel, for steps of single tokens (H rows per
+// request: one tile of 16 for up to 16 heads): described where it stands; the keys are cut into `splits` ranges over
 // blockIdx.z whose partial results (float32, with the base-2 logarithm of their sums) the shared merge kernel adds.
+// In both, shared-memory rows are D_K + 8 elements apart, which puts the eight rows of an ldmatrix into eight different
+// bank groups for every D_K that is a multiple of 16, and a key row's page is looked up once per tile at most.
 #include "common.cuh"
 #include "mma_common.cuh"
 
