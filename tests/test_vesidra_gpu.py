@@ -421,6 +421,28 @@ def test_cuttings_against_plain(tmp_path, request, dtype, name, page_size, cutti
     assert not runtime.manager.requests and all(a.free_count == a.num_pages for a in runtime.manager.allocators)
 
 
+@pytest.mark.parametrize("name,page_size", [("a", 8), ("c", 16)])
+def test_float32_logits_do_not_depend_on_cutting_or_batch(tmp_path, name, page_size):
+    """In float32 every sum has an order that depends on the position alone (products with one thread per element, keys in
+    blocks from absolute key 0, routed rows computed independently), so a request alone and whole, in portions, and
+    batched with others on other pages must give the same logits to the last bit or two: far tighter than the bound
+    against the plain implementation, and independent of it."""
+    folder = vh.make_folder(tmp_path, name, seed=16)
+    vocab = vh.CONFIGS[name]["vocab"]
+    requests = {f"r{i}": helpers.random_tokens(vocab, n, seed=900 + i) for i, n in enumerate((1, 9, 33, 64, 65, 150))}
+    results = {}
+    for cutting in ("whole", "portions", "mixed"):
+        steps = CUTTINGS[cutting](requests)
+        runtime = build(folder, "float32", helpers.max_live_tokens(steps, granule=64) // page_size, page_size)
+        results[cutting] = helpers.collect(steps, replay(runtime, steps))
+    for rid, tokens in requests.items():
+        for position in range(len(tokens)):
+            alone = results["whole"][rid][position]
+            scale = max(1.0, float(alone.abs().max()))
+            for cutting in ("portions", "mixed"):
+                assert float((results[cutting][rid][position] - alone).abs().max()) <= 1e-6 * scale, (rid, position, cutting)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["a", "c"])
 def test_prefill_against_decoding_every_token(tmp_path, dtype, name):
