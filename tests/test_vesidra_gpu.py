@@ -132,6 +132,39 @@ def test_latent_attention_kernel(dtype, heads, rank, rot, page, window, single):
     assert torch.allclose(out.double().cpu(), expected, **tol(dtype, float(expected.abs().max())))
 
 
+@pytest.mark.parametrize("heads,rank,rot,page", [(16, 256, 32, 16), (6, 128, 32, 64), (20, 64, 16, 8), (16, 512, 64, 16), (3, 96, 0, 4)])
+def test_latent_attention_decode_over_long_contexts(heads, rank, rot, page):
+    """A decode step over contexts of thousands of tokens: the keys are cut into many ranges (up to 32, more than the
+    merge kernel's usual form takes), blocks walk many tiles through all their key buffers, and the part of the page
+    table that a block keeps in shared memory is long.  One key far back stands out in every request."""
+    from miniserve_b200 import kernels
+
+    dtype, dk = torch.bfloat16, rank + rot
+    lens = [3000, 2111, 5]
+    total_pages = sum((l + page - 1) // page for l in lens)
+    order = torch.randperm(total_pages, generator=torch.Generator().manual_seed(3)).tolist()
+    width = max((l + page - 1) // page for l in lens)
+    tables, next_page = [], 0
+    for l in lens:
+        count = (l + page - 1) // page
+        tables.append(order[next_page:next_page + count] + [0] * (width - count))
+        next_page += count
+    cache = rand((total_pages, page, dk), dtype, 21, 0.5)
+    q = rand((len(lens), heads, dk), dtype, 22, 0.5)
+    for r, l in enumerate(lens):                      # key 7 of every request points where the request's first head looks
+        cache[tables[r][7 // page], 7 % page] = (q[r, 0].float() * 3.0).to(dtype)
+    args = [torch.tensor(tables, dtype=torch.int32).cuda(), torch.arange(len(lens), dtype=torch.int32).cuda(),
+            torch.tensor([l - 1 for l in lens], dtype=torch.int32).cuda(), torch.arange(len(lens) + 1, dtype=torch.int32).cuda(),
+            torch.tensor(lens, dtype=torch.int32).cuda()]
+    out = torch.empty((len(lens), heads, rank), dtype=dtype).cuda()
+    kernels.latent_attention(q, cache, *args, 1, max(lens), rank, 0.3, None, out)
+    expected = torch.zeros((len(lens), heads, rank), dtype=torch.float64)
+    plain_ops.latent_attention(q.cpu(), cache.cpu(), *(a.cpu() for a in args), 1, max(lens), rank, 0.3, None, expected)
+    assert torch.allclose(out.double().cpu(), expected, **tol(dtype, float(expected.abs().max())))
+    far = cache[tables[0][7 // page], 7 % page, :rank].double().cpu()
+    assert float((expected[0, 0] - far).abs().max()) < 0.05 * float(far.abs().max())      # the far key decides head 0
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_head_gate_and_batched_product(dtype):
     from miniserve_b200 import kernels
