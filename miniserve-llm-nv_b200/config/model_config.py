@@ -288,3 +288,189 @@ class VesidraConfig:
             layers.append(dict(type=layer.type, mixer=mixer, mlp=mlp))
         return dict(architecture=self.architecture, vocab=self.vocab, width=self.width,
                     embedding=dict(scale=self.embedding_scale), norm=dict(eps=self.eps), layers=layers)
+
+
+# --------------------------------------------------------------------------- Zozezen
+
+
+def _count(data: Mapping[str, Any], key: str, default: int) -> int:
+    """An integer that may be absent or null (then ``default``) and may be zero."""
+    value = data.get(key)
+    if value is None:
+        return default
+    if not isinstance(value, int) or isinstance(value, bool) or value < 0:
+        raise ValueError(f"{key} must be a non-negative integer in the model config, got {value!r}")
+    return value
+
+
+@dataclass(frozen=True)
+class GatedAttentionConfig:
+    """Grouped-query attention with query/key heads of ``dim`` and value heads of ``vdim`` entries, a rotation over the
+    first ``rot.dims`` entries, a sink in the softmax and a gate per head.  ``kv_from``: the index of the layer whose
+    keys and values this layer reads instead of making its own (None: its own)."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    rot: RotationConfig
+    kv_from: Any = None
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], where: str) -> "GatedAttentionConfig":
+        config = cls(heads=_integer(data, "heads"), kv_heads=_integer(data, "kv_heads"), dim=_integer(data, "dim"),
+                     vdim=_integer(data, "vdim"), scale=_positive(data, "scale", where),
+                     rot=RotationConfig.from_dict(_section(data, "rot", where), where + "rot."),
+                     kv_from=None if data.get("kv_from") is None else _count(data, "kv_from", 0))
+        if config.heads % config.kv_heads:
+            raise ValueError(f"{where}heads {config.heads} is not a multiple of kv_heads {config.kv_heads}")
+        if config.rot.dims > config.dim:
+            raise ValueError(f"{where}rot.dims {config.rot.dims} exceeds the head size dim {config.dim}")
+        if config.rot.scaling is not None:
+            raise UnsupportedModelError(f"UNSUPPORTED_MODEL_CONFIGURATION: {where}rot.scaling is not part of this design")
+        return config
+
+    def to_dict(self) -> dict[str, Any]:
+        out = dict(heads=self.heads, kv_heads=self.kv_heads, dim=self.dim, vdim=self.vdim, scale=self.scale,
+                   rot=dict(base=self.rot.base, dims=self.rot.dims))
+        if self.kv_from is not None:
+            out["kv_from"] = self.kv_from
+        return out
+
+
+@dataclass(frozen=True)
+class StateSpaceConfig:
+    """The selective state-space mixer: ``heads`` heads of ``vdim`` channels, a state of ``state`` numbers per channel,
+    ``groups`` groups of input and output maps shared by ``heads / groups`` heads each, a causal convolution of ``conv``
+    taps, and a gated norm in ``norm_groups`` equal parts."""
+
+    heads: int
+    vdim: int
+    state: int
+    groups: int
+    conv: int
+    norm_groups: int
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], where: str) -> "StateSpaceConfig":
+        config = cls(heads=_integer(data, "heads"), vdim=_integer(data, "vdim"), state=_integer(data, "state"),
+                     groups=_integer(data, "groups"), conv=_integer(data, "conv"), norm_groups=_integer(data, "norm_groups"))
+        if config.heads % config.groups:
+            raise ValueError(f"{where}heads {config.heads} is not a multiple of groups {config.groups}")
+        if (config.heads * config.vdim) % config.norm_groups:
+            raise ValueError(f"{where}norm_groups {config.norm_groups} does not divide heads * vdim = {config.heads * config.vdim}")
+        return config
+
+    def to_dict(self) -> dict[str, Any]:
+        return dict(heads=self.heads, vdim=self.vdim, state=self.state, groups=self.groups, conv=self.conv,
+                    norm_groups=self.norm_groups)
+
+
+@dataclass(frozen=True)
+class GroupedMixtureConfig:
+    """A mixture of ``experts`` clamped gated experts of inner size ``ff`` plus ``identity`` identity experts, of which a
+    token uses ``top``; the router's outputs form ``group_count`` equal groups of neighbours of which the best
+    ``group_keep`` can be chosen from; a shared expert of inner size ``shared_ff`` (None: no shared expert)."""
+
+    ff: int
+    limit: float
+    experts: int
+    identity: int
+    top: int
+    group_count: int
+    group_keep: int
+    shared_ff: Any = None
+    shared_limit: Any = None
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], where: str) -> "GroupedMixtureConfig":
+        kind = data.get("kind", "moe")
+        if kind != "moe":
+            raise UnsupportedModelError(f"UNSUPPORTED_MODEL_CONFIGURATION: {where}kind {kind!r} is not implemented (moe)")
+        expert, router = _section(data, "expert", where), _section(data, "router", where)
+        groups = router.get("groups")
+        count, keep = 1, 1
+        if groups is not None:
+            groups = _section(router, "groups", where + "router.")
+            count, keep = _integer(groups, "count"), _integer(groups, "keep")
+        shared = data.get("shared")
+        if shared is not None:
+            shared = _section(data, "shared", where)
+        config = cls(ff=_integer(expert, "ff"), limit=_positive(expert, "limit", where + "expert."),
+                     experts=_integer(router, "experts"), identity=_count(router, "identity", 0), top=_integer(router, "top"),
+                     group_count=count, group_keep=keep,
+                     shared_ff=None if shared is None else _integer(shared, "ff"),
+                     shared_limit=None if shared is None else _positive(shared, "limit", where + "shared."))
+        total = config.experts + config.identity
+        if total % config.group_count or not 1 <= config.group_keep <= config.group_count:
+            raise ValueError(f"{where}router.groups: {total} router outputs in {config.group_count} groups, {config.group_keep} kept")
+        if config.top > config.group_keep * (total // config.group_count):
+            raise ValueError(f"{where}router.top {config.top} exceeds the {config.group_keep} kept groups of {total // config.group_count}")
+        return config
+
+    def to_dict(self) -> dict[str, Any]:
+        router = dict(experts=self.experts, identity=self.identity, top=self.top,
+                      groups=dict(count=self.group_count, keep=self.group_keep))
+        shared = None if self.shared_ff is None else dict(ff=self.shared_ff, limit=self.shared_limit)
+        return dict(kind="moe", expert=dict(ff=self.ff, limit=self.limit), router=router, shared=shared)
+
+
+@dataclass(frozen=True)
+class ZozezenLayerConfig:
+    type: str       # "attention" or "mamba2"
+    mixer: Any      # GatedAttentionConfig or StateSpaceConfig
+    mlp: Any        # GroupedMixtureConfig or None
+
+
+@dataclass(frozen=True)
+class ZozezenConfig:
+    """The Zozezen decoder: ``config.json`` holds ``architecture``, ``vocab``, ``width``, ``norm.eps`` and ``layers``, a
+    list whose entries give each layer's mixer ``type`` (``attention`` or ``mamba2``), the mixer's sizes and constants
+    (``mixer``) and its feed-forward (``mlp``, or null).  Every size and constant is read; nothing is inferred."""
+
+    vocab: int
+    width: int
+    eps: float
+    layers: tuple
+    architecture: str = "Zozezen"
+
+    MIXERS = {"attention": GatedAttentionConfig, "mamba2": StateSpaceConfig}
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any]) -> "ZozezenConfig":
+        if data.get("architecture") != "Zozezen":
+            raise UnsupportedModelError(f"UNSUPPORTED_MODEL_CONFIGURATION: expected architecture 'Zozezen', got {data.get('architecture')!r}")
+        raw_layers = data.get("layers")
+        if not isinstance(raw_layers, (list, tuple)) or not raw_layers:
+            raise ValueError("layers must be a non-empty list in the model config")
+        layers = []
+        for index, raw in enumerate(raw_layers):
+            where = f"layers[{index}]."
+            if not isinstance(raw, Mapping):
+                raise ValueError(f"layers[{index}] must be an object")
+            kind = raw.get("type")
+            if kind not in cls.MIXERS:
+                raise UnsupportedModelError(f"UNSUPPORTED_MODEL_CONFIGURATION: {where}type {kind!r} is not implemented "
+                                            f"({', '.join(cls.MIXERS)})")
+            mixer = cls.MIXERS[kind].from_dict(_section(raw, "mixer", where), where + "mixer.")
+            mlp = None if raw.get("mlp") is None else GroupedMixtureConfig.from_dict(_section(raw, "mlp", where), where + "mlp.")
+            layers.append(ZozezenLayerConfig(kind, mixer, mlp))
+        for index, layer in enumerate(layers):
+            source = getattr(layer.mixer, "kv_from", None)
+            if source is None:
+                continue
+            where = f"layers[{index}].mixer.kv_from"
+            if not source < index or layers[source].type != "attention" or layers[source].mixer.kv_from is not None:
+                raise ValueError(f"{where} {source} must name an earlier attention layer that has keys and values of its own")
+            lender, m = layers[source].mixer, layer.mixer
+            if (lender.kv_heads, lender.dim, lender.vdim, lender.rot) != (m.kv_heads, m.dim, m.vdim, m.rot):
+                raise ValueError(f"{where}: layer {source}'s key/value heads, sizes and rotation differ from this layer's")
+        return cls(vocab=_integer(data, "vocab"), width=_integer(data, "width"),
+                   eps=_positive(_section(data, "norm", ""), "eps", "norm."), layers=tuple(layers))
+
+    def to_dict(self) -> dict[str, Any]:
+        """The ``config.json`` content that reads back as this configuration."""
+        layers = [dict(type=layer.type, mixer=layer.mixer.to_dict(), mlp=None if layer.mlp is None else layer.mlp.to_dict())
+                  for layer in self.layers]
+        return dict(architecture=self.architecture, vocab=self.vocab, width=self.width, norm=dict(eps=self.eps), layers=layers)

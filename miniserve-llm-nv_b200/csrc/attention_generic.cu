@@ -15,6 +15,11 @@
 // Two optional changes of a score s between query position p and key position j, applied in this
 // order before the softmax: a soft cap, s = cap * tanh(s / cap); and a bias that grows with the
 // distance, s += slope[head] * (j - p) (one slope per query head; zero at the query's own key).
+//
+// Three more options.  Value heads may have another size dv than query and key heads (d): the pools then differ in
+// their last dimension and the output has dv numbers per head.  `sink`: the softmax's denominator gets one more term
+// exp(0), a key of score 0 without a value, p_j = exp(s_j) / (1 + sum exp(s_j)).  `gate`: the head's output is
+// multiplied by sigmoid(gate[token, head]) as it is stored.
 #include "common.cuh"
 
 namespace ms {
@@ -65,13 +70,14 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T*
                                                int table_stride, const int* __restrict__ request_of_token,
                                                const int* __restrict__ positions, int page_size, int n_q, int n_kv,
                                                int d, float scale, int window, float softcap,
-                                               const float* __restrict__ bias_slopes, T* __restrict__ out) {
+                                               const float* __restrict__ bias_slopes, T* __restrict__ out, int dv,
+                                               int sink, const T* __restrict__ gate, int gate_ld) {
   grid_dependency_wait();
   grid_dependency_launch();
   extern __shared__ float smem[];
   float* q_s = smem;                                  // [d]
-  float* part_acc = smem + d;                         // [warps][d]
-  float* part_m = part_acc + kAttnWarps * d;          // [warps]
+  float* part_acc = smem + d;                         // [warps][dv]
+  float* part_m = part_acc + kAttnWarps * dv;         // [warps]
   float* part_l = part_m + kAttnWarps;                // [warps]
 
   const int token = blockIdx.x, head = blockIdx.y;
@@ -100,8 +106,8 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T*
     size_t row_offset = 0;
     if (valid) {
       const int page = table[key / page_size];
-      row_offset = (((size_t)page * n_kv + kv_head) * page_size + key % page_size) * d;
-      score = dot_row(q_s, k_pool + row_offset, d);
+      row_offset = ((size_t)page * n_kv + kv_head) * page_size + key % page_size;      // the row's index in both pools
+      score = dot_row(q_s, k_pool + row_offset * d, d);
       if (softcap > 0.f) score = softcap * tanhf(score / softcap);
       score += slope * (float)(key - pos);
     }
@@ -117,11 +123,11 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T*
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const size_t off_j = __shfl_sync(0xffffffffu, (unsigned long long)row_offset, j);
       if (pj == 0.f) continue;   // uniform across the warp
-      const T* v_row = v_pool + off_j;
+      const T* v_row = v_pool + off_j * dv;
 #pragma unroll
       for (int i = 0; i < kMaxLanesPerThread; ++i) {
         const int c = lane + 32 * i;
-        if (c < d) acc[i] += pj * to_float(v_row[c]);
+        if (c < dv) acc[i] += pj * to_float(v_row[c]);
       }
     }
   }
@@ -133,19 +139,22 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T*
 #pragma unroll
   for (int i = 0; i < kMaxLanesPerThread; ++i) {
     const int c = lane + 32 * i;
-    if (c < d) part_acc[warp * d + c] = acc[i];
+    if (c < dv) part_acc[warp * dv + c] = acc[i];
   }
   __syncthreads();
-  float m_all = -INFINITY;
+  float m_all = sink ? 0.f : -INFINITY;               // the sink is a key of score 0
   for (int w = 0; w < kAttnWarps; ++w) m_all = fmaxf(m_all, part_m[w]);
   float l_all = 0.f;
   for (int w = 0; w < kAttnWarps; ++w) l_all += part_m[w] == -INFINITY ? 0.f : part_l[w] * expf(part_m[w] - m_all);
-  T* out_row = out + ((size_t)token * n_q + head) * d;
-  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+  if (sink) l_all += expf(-m_all);
+  float factor = 1.f / l_all;
+  if (gate) factor /= 1.f + expf(-to_float(gate[(size_t)token * gate_ld + head]));
+  T* out_row = out + ((size_t)token * n_q + head) * dv;
+  for (int c = threadIdx.x; c < dv; c += blockDim.x) {
     float sum = 0.f;
     for (int w = 0; w < kAttnWarps; ++w)
-      if (part_m[w] != -INFINITY) sum += part_acc[w * d + c] * expf(part_m[w] - m_all);
-    out_row[c] = from_float<T>(sum / l_all);
+      if (part_m[w] != -INFINITY) sum += part_acc[w * dv + c] * expf(part_m[w] - m_all);
+    out_row[c] = from_float<T>(sum * factor);
   }
 }
 
@@ -157,30 +166,35 @@ using namespace ms;
 // [requests, table_stride]; request_of_token, positions [n_tokens]; out [n_tokens, n_q, d].
 // The keys of a token are positions max(0, pos - window + 1) .. pos of its own request
 // (window <= 0: no window); they must already be in the pool.  softcap <= 0: no soft cap; bias_slopes
-// [n_q] float32 or null.
+// [n_q] float32 or null.  dv: the size of a value head (value pool [pages, n_kv, page_size, dv], out [n_tokens, n_q, dv]);
+// sink != 0: one more term exp(0) in the softmax's denominator; gate (null: none): logits of the model's element type,
+// gate[token * gate_ld + head], whose sigmoid multiplies the head's output.
 MS_EXPORT int ms_paged_attention_generic(const void* q, int dtype, const void* k_pool, const void* v_pool,
                                          const int* block_tables, int table_stride, const int* request_of_token,
                                          const int* positions, int page_size, int n_q, int n_kv, int d, float scale,
                                          int window, float softcap, const float* bias_slopes, void* out, int n_tokens,
-                                         cudaStream_t stream) {
+                                         int dv, int sink, const void* gate, int gate_ld, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   MS_REQUIRE(d > 0 && d <= 32 * kMaxLanesPerThread, "paged_attention: head size %d outside 1..%d", d,
+             32 * kMaxLanesPerThread);
+  MS_REQUIRE(dv > 0 && dv <= 32 * kMaxLanesPerThread, "paged_attention: value head size %d outside 1..%d", dv,
              32 * kMaxLanesPerThread);
   MS_REQUIRE(n_kv > 0 && n_q % n_kv == 0, "paged_attention: %d query heads are not a multiple of %d key/value heads",
              n_q, n_kv);
   MS_REQUIRE(page_size > 0, "paged_attention: page size must be positive, got %d", page_size);
   MS_REQUIRE(n_q <= 65535, "paged_attention: %d query heads exceed 65535", n_q);
-  const size_t smem = (size_t)(d + kAttnWarps * d + 2 * kAttnWarps) * sizeof(float);
+  const size_t smem = (size_t)(d + kAttnWarps * dv + 2 * kAttnWarps) * sizeof(float);
   dim3 grid(n_tokens, n_q);
   if (dtype == MS_F32) {
     ms::launch(paged_attention_generic_kernel<float>, grid, kAttnWarps * 32, smem, stream, 
         (const float*)q, (const float*)k_pool, (const float*)v_pool, block_tables, table_stride, request_of_token,
-        positions, page_size, n_q, n_kv, d, scale, window, softcap, bias_slopes, (float*)out);
+        positions, page_size, n_q, n_kv, d, scale, window, softcap, bias_slopes, (float*)out, dv, sink,
+        (const float*)gate, gate_ld);
   } else if (dtype == MS_BF16) {
     ms::launch(paged_attention_generic_kernel<__nv_bfloat16>, grid, kAttnWarps * 32, smem, stream, 
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, block_tables,
         table_stride, request_of_token, positions, page_size, n_q, n_kv, d, scale, window, softcap, bias_slopes,
-        (__nv_bfloat16*)out);
+        (__nv_bfloat16*)out, dv, sink, (const __nv_bfloat16*)gate, gate_ld);
   } else {
     MS_FAIL("paged_attention: unknown element type code %d", dtype);
   }

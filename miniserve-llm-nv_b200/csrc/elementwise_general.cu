@@ -1,0 +1,181 @@
+// More memory-bound kernels between the matrix products, for blocks and mixers whose forms elementwise.cu does not cover:
+//
+//   ms_postnorm_add_rmsnorm   a sublayer's output is RMS-normed with a weight of its own, added to the float32 residual
+//                             stream, and the stream is RMS-normed for the next sublayer: one kernel, one pass over the row
+//   ms_qkv_prepare            per-head norm, partial half-split rotation and paged append for a projection whose columns are
+//                             laid out freely: query heads of d numbers, key heads of d, value heads of dv (another size),
+//                             or queries alone (a layer that reads another layer's keys and values)
+//
+// All arithmetic is float32; storage is float32 or bfloat16.
+#include "common.cuh"
+
+namespace ms {
+
+// For output row k (source row r = rows ? rows[k] : k):
+//   a = post_weight * delta[r] / sqrt(mean(delta[r]^2) + post_eps)
+//   x = residual[r] + a            (float32; written back to residual unless rows are gathered)
+//   out[k] = weight * x / sqrt(mean(x^2) + eps)     rounded once to T
+// The row (width <= blockDim.x * kPostNormPerThread) stays in registers between the passes.
+constexpr int kPostNormPerThread = 16;
+
+template <typename T>
+__global__ void postnorm_add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                            const void* __restrict__ post_weight, int post_weight_dtype, float post_eps,
+                                            const void* __restrict__ weight, int weight_dtype, float eps,
+                                            const int* __restrict__ rows, T* __restrict__ out, int hidden) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  __shared__ float scratch[32];
+  const size_t k = blockIdx.x;
+  const size_t r = rows ? (size_t)rows[k] : k;
+  float* res = residual + r * hidden;
+  const T* del = delta + r * hidden;
+  float v[kPostNormPerThread];
+  float sum_sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < kPostNormPerThread; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    v[i] = c < hidden ? to_float(del[c]) : 0.f;
+    sum_sq += v[i] * v[i];
+  }
+  const float inv_delta = 1.0f / sqrtf(block_sum(sum_sq, scratch) / (float)hidden + post_eps);
+  sum_sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < kPostNormPerThread; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < hidden) {
+      v[i] = res[c] + load_as_float(post_weight, post_weight_dtype, c) * (v[i] * inv_delta);
+      if (rows == nullptr) res[c] = v[i];
+      sum_sq += v[i] * v[i];
+    }
+  }
+  const float inv = 1.0f / sqrtf(block_sum(sum_sq, scratch) / (float)hidden + eps);
+  T* dst = out + k * hidden;
+#pragma unroll
+  for (int i = 0; i < kPostNormPerThread; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < hidden) dst[c] = from_float<T>(load_as_float(weight, weight_dtype, c) * (v[i] * inv));
+  }
+}
+
+// One warp per (token, head) of proj[n, ld]: query head h at columns q_col + h d, key head g at k_col + g d, value head
+// g at v_col + g dv (k_col < 0: the projection holds no keys and values).
+//   q heads: optional RMS norm over d (weight float32), rotation, written to q_out[n, h, :]
+//   k heads: the same with their own weight, written to the key pool [page, kv_head, page_size, d] at the token's slot
+//   v heads: copied to the value pool [page, kv_head, page_size, dv]
+// Rotation: the first rotary_dim entries of a head, entry i paired with entry i + rotary_dim / 2; the pair (u, v)
+// becomes (u cos - v sin, v cos + u sin) with (cos, sin) = cos_sin[n, i].  A negative slot skips the writes.
+template <typename T>
+__global__ void qkv_prepare_kernel(const T* __restrict__ proj, int ld, int q_col, int k_col, int v_col, int n_q, int n_kv,
+                                   int d, int dv, const int* __restrict__ slots, const float* __restrict__ q_weight,
+                                   const float* __restrict__ k_weight, float eps, const float2* __restrict__ cos_sin,
+                                   int rotary_dim, T* __restrict__ k_pool, T* __restrict__ v_pool, int page_size,
+                                   T* __restrict__ q_out, int n_tokens) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  extern __shared__ float prepare_smem[];
+  const int warps_per_block = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = n_q + (k_col >= 0 ? 2 * n_kv : 0);
+  const long long item = (long long)blockIdx.x * warps_per_block + warp;
+  if (item >= (long long)n_tokens * heads) return;
+  const int n = (int)(item / heads), head = (int)(item % heads);
+  const T* row = proj + (size_t)n * ld;
+  float* x = prepare_smem + warp * d;
+
+  const T* src;
+  T* dst;
+  const float* weight;
+  if (head < n_q) {
+    src = row + q_col + head * d;
+    dst = q_out + ((size_t)n * n_q + head) * d;
+    weight = q_weight;
+  } else {
+    const int slot = slots[n];
+    if (slot < 0) return;
+    const int page = slot / page_size, offset = slot % page_size;
+    if (head >= n_q + n_kv) {
+      const int g = head - n_q - n_kv;
+      src = row + v_col + g * dv;
+      dst = v_pool + (((size_t)page * n_kv + g) * page_size + offset) * dv;
+      for (int c = lane; c < dv; c += 32) dst[c] = src[c];
+      return;
+    }
+    const int g = head - n_q;
+    src = row + k_col + g * d;
+    dst = k_pool + (((size_t)page * n_kv + g) * page_size + offset) * d;
+    weight = k_weight;
+  }
+  float sum_sq = 0.f;
+  for (int c = lane; c < d; c += 32) {
+    const float v = to_float(src[c]);
+    x[c] = v;
+    sum_sq += v * v;
+  }
+  float inv = 1.f;
+  if (weight) inv = 1.0f / sqrtf(warp_sum(sum_sq) / (float)d + eps);
+  __syncwarp();
+  const int half = rotary_dim >> 1;
+  const float2* table = cos_sin ? cos_sin + (size_t)n * half : nullptr;
+  for (int c = lane; c < d; c += 32) {
+    float v = x[c] * inv;
+    if (weight) v *= weight[c];
+    if (table && c < rotary_dim) {
+      const int j = c < half ? c : c - half;
+      const int partner = c < half ? c + half : c - half;
+      float other = x[partner] * inv;
+      if (weight) other *= weight[partner];
+      const float2 cs = table[j];
+      v = c < half ? v * cs.x - other * cs.y : v * cs.x + other * cs.y;
+    }
+    dst[c] = from_float<T>(v);
+  }
+}
+
+}  // namespace ms
+
+using namespace ms;
+
+#define MS_EG_DISPATCH(dtype, ...)                               \
+  if ((dtype) == MS_F32) { using T = float; __VA_ARGS__; }       \
+  else if ((dtype) == MS_BF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
+  else MS_FAIL("unknown element type code %d", (dtype));
+
+// residual float32 [rows, hidden]; delta [rows, hidden] and out [n_out, hidden] of type `dtype`; the two weights [hidden]
+// in their own types; rows int32 [n_out] or null (then n_out rows in place, and the residual receives the sum).
+MS_EXPORT int ms_postnorm_add_rmsnorm(float* residual, const void* delta, int dtype, const void* post_weight,
+                                      int post_weight_dtype, float post_eps, const void* weight, int weight_dtype, float eps,
+                                      const int* rows, void* out, int n_out, int hidden, cudaStream_t stream) {
+  if (n_out == 0) return 0;
+  MS_REQUIRE(hidden > 0 && hidden <= 1024 * kPostNormPerThread, "postnorm_add_rmsnorm: width %d outside 1..%d", hidden,
+             1024 * kPostNormPerThread);
+  int threads = ((hidden + kPostNormPerThread - 1) / kPostNormPerThread + 31) / 32 * 32;
+  if (threads < 128 && hidden >= 128) threads = 128;
+  if (hidden >= 2048 && threads < 256) threads = 256;
+  MS_EG_DISPATCH(dtype, (ms::launch(postnorm_add_rmsnorm_kernel<T>, n_out, threads, 0, stream, residual, (const T*)delta,
+                                    post_weight, post_weight_dtype, post_eps, weight, weight_dtype, eps, rows, (T*)out, hidden)));
+  MS_CHECK_LAUNCH("postnorm_add_rmsnorm");
+  return 0;
+}
+
+MS_EXPORT int ms_qkv_prepare(const void* proj, int dtype, int ld, int q_col, int k_col, int v_col, int n_q, int n_kv, int d,
+                             int dv, const int* slots, const float* q_weight, const float* k_weight, float eps,
+                             const float* cos_sin, int rotary_dim, void* k_pool, void* v_pool, int page_size, void* q_out,
+                             int n_tokens, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  MS_REQUIRE(d > 0 && d <= 1024 && dv > 0, "qkv_prepare: head sizes %d and %d", d, dv);
+  MS_REQUIRE(rotary_dim >= 0 && rotary_dim <= d && rotary_dim % 2 == 0,
+             "qkv_prepare: rotary size %d must be even and at most the head size %d", rotary_dim, d);
+  MS_REQUIRE(page_size > 0, "qkv_prepare: page size must be positive, got %d", page_size);
+  MS_REQUIRE(k_col < 0 || (v_col >= 0 && slots && k_pool && v_pool), "qkv_prepare: keys and values need their columns, slots and pools");
+  const int warps = 4;
+  const long long items = (long long)n_tokens * (n_q + (k_col >= 0 ? 2 * n_kv : 0));
+  const long long blocks = (items + warps - 1) / warps;
+  MS_REQUIRE(blocks < 2147483647LL, "qkv_prepare: %lld heads in one launch is too many", items);
+  const size_t smem = (size_t)warps * d * sizeof(float);
+  MS_EG_DISPATCH(dtype, (ms::launch(qkv_prepare_kernel<T>, (unsigned)blocks, warps * 32, smem, stream, (const T*)proj, ld, q_col,
+                                    k_col, v_col, n_q, n_kv, d, dv, slots, q_weight, k_weight, eps, (const float2*)cos_sin,
+                                    rotary_dim, (T*)k_pool, (T*)v_pool, page_size, (T*)q_out, n_tokens)));
+  MS_CHECK_LAUNCH("qkv_prepare");
+  return 0;
+}

@@ -9,6 +9,15 @@
 //                       product of an expert), optional squared-ReLU on the results
 //   ms_expert_combine   out[token] = sum over its choices of weight * result row (+ a shared expert's output)
 //   ms_relu_square      x = max(x, 0)^2 in place
+//   ms_router_choose    another way to route: scores are the softmax over ALL router outputs, a correction is added for the
+//                       choice only, the outputs form groups of which only the best can be chosen from, and the weights are
+//                       the chosen scores as they are
+//   ms_clamped_glu      out = g sigmoid(1.702 g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit) for
+//                       alternating (gate, up) columns; the same activation is an epilogue of ms_expert_linear
+//
+// An expert id at or above the number of experts with weights stands for an identity expert (its output is its input):
+// ms_expert_route sorts such pairs behind the others, ms_expert_linear is given the smaller expert count and never
+// touches them, and ms_expert_combine reads the token's own row for them.
 //
 // The products accumulate in float32.  The float32 form has one thread per output element summing k in ascending order;
 // the bfloat16 form runs on the tensor cores.  In both a row's result depends on the row and its expert alone, not on
@@ -134,6 +143,83 @@ __global__ void router_select_kernel(const float* __restrict__ all_logits, int e
   for (int k = lane; k < top; k += 32) weights[(size_t)n * top + k] = expf(taken[k] - peak) / total;
 }
 
+// One warp per token.  scores = softmax over the first `total` logits of the row; choice = score + correction; the
+// outputs form `group_count` equal groups of neighbours, a group's score is its largest choice score, and only members of
+// the `group_keep` best groups (ties: the lower group) can be chosen; the `top` largest choice scores among those are
+// taken one after the other (ties: the lower index); weights are the taken outputs' scores, not renormalised.  A choice
+// score that is not a number counts as the smallest, so that every id written is a valid one.
+__global__ void router_choose_kernel(const float* __restrict__ all_logits, int ld, int total, int top,
+                                     const float* __restrict__ correction, int group_count, int group_keep,
+                                     int* __restrict__ ids, float* __restrict__ weights, int n_tokens) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  extern __shared__ float select_smem[];
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* score = select_smem + (size_t)warp * (2 * total + group_count);
+  float* choice = score + total;
+  float* group_best = choice + total;
+  const int n = blockIdx.x * warps + warp;
+  if (n >= n_tokens) return;
+  const float* logits = all_logits + (size_t)n * ld;
+  float peak = -INFINITY;
+  for (int e = lane; e < total; e += 32) peak = fmaxf(peak, logits[e]);
+  peak = warp_max(peak);
+  float sum = 0.f;
+  for (int e = lane; e < total; e += 32) {
+    const float v = expf(logits[e] - peak);
+    score[e] = v;
+    sum += v;
+  }
+  sum = warp_sum(sum);
+  __syncwarp();
+  for (int e = lane; e < total; e += 32) {
+    const float v = score[e] / sum;
+    score[e] = v;
+    float c = v + (correction ? correction[e] : 0.f);
+    if (!(c == c)) c = -3.0e38f;
+    choice[e] = fmaxf(c, -3.0e38f);
+  }
+  __syncwarp();
+  const int per_group = total / group_count;
+  if (group_keep < group_count) {
+    for (int g = lane; g < group_count; g += 32) {
+      float best = -INFINITY;
+      for (int i = 0; i < per_group; ++i) best = fmaxf(best, choice[g * per_group + i]);
+      group_best[g] = best;
+    }
+    __syncwarp();
+    // a group is kept if fewer than `group_keep` groups come before it (a larger score, or the same with a lower index)
+    for (int g = lane; g < group_count; g += 32) {
+      const float mine = group_best[g];
+      int before = 0;
+      for (int o = 0; o < group_count; ++o) before += (group_best[o] > mine || (group_best[o] == mine && o < g)) ? 1 : 0;
+      if (before >= group_keep)
+        for (int i = 0; i < per_group; ++i) choice[g * per_group + i] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+    for (int e = lane; e < total; e += 32) {
+      const float v = choice[e];
+      if (v > best) { best = v; best_e = e; }       // ascending e: the lower index wins a tie
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, o);
+      const int other_e = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (other > best || (other == best && other_e < best_e)) { best = other; best_e = other_e; }
+    }
+    if (lane == 0) {
+      ids[(size_t)n * top + k] = best_e;
+      weights[(size_t)n * top + k] = score[best_e];
+      choice[best_e] = -INFINITY;
+    }
+    __syncwarp();
+  }
+}
+
 // One block.  offsets[e] .. offsets[e + 1] is expert e's segment of the sorted order; order[i] is the pair (token * top
 // + choice) at place i, place[pair] its place.  Within a segment the order is arbitrary: rows are computed independently.
 __global__ void expert_route_kernel(const int* __restrict__ ids, int pairs, int experts, int* __restrict__ offsets,
@@ -166,13 +252,23 @@ __global__ void expert_route_kernel(const int* __restrict__ ids, int pairs, int 
 
 constexpr int EBM = 64, EBN = 64, EBK = 16, ETM = 4, ETN = 4;
 
+// epilogues of the experts' products
+enum : int { kActNone = 0, kActReluSquare = 1, kActClampedGlu = 2 };
+
+// g = min(gate, limit), u = clamp(up, -limit, limit); g sigmoid(1.702 g) (u + 1)
+__device__ __forceinline__ float clamped_glu(float gate, float up, float limit) {
+  const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+  return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+}
+
 // C[i, :] = act(A[src(i), :] W_e^T) for every place i of expert e's segment; W [experts, N, K].  blockIdx.y walks the
 // row tiles of all segments one after the other (a segment's last tile may be partial); tiles beyond the last do nothing.
 // src(i) = order[i] / top with `order` (rows gathered from the tokens), else i.
 template <typename T>
 __global__ void __launch_bounds__(256)
 expert_linear_kernel(const T* __restrict__ A, int lda, const int* __restrict__ order, int top, const T* __restrict__ W,
-                     T* __restrict__ C, int ldc, const int* __restrict__ offsets, int experts, int N, int K, int relu_square) {
+                     T* __restrict__ C, int ldc, const int* __restrict__ offsets, int experts, int N, int K, int activation,
+                     float limit) {
   grid_dependency_wait();
   grid_dependency_launch();
   __shared__ float As[EBK][EBM + 4];
@@ -226,12 +322,20 @@ expert_linear_kernel(const T* __restrict__ A, int lda, const int* __restrict__ o
   for (int i = 0; i < ETM; ++i) {
     const int m = m0 + ty * ETM + i;
     if (m >= end) continue;
+    if (activation == kActClampedGlu) {           // columns alternate (gate, up): two of them give one result
+#pragma unroll
+      for (int j = 0; j < ETN; j += 2) {
+        const int n = n0 + tx * ETN + j;
+        if (n + 1 < N) C[(size_t)m * ldc + n / 2] = from_float<T>(clamped_glu(acc[i][j], acc[i][j + 1], limit));
+      }
+      continue;
+    }
 #pragma unroll
     for (int j = 0; j < ETN; ++j) {
       const int n = n0 + tx * ETN + j;
       if (n >= N) continue;
       float v = acc[i][j];
-      if (relu_square) { v = fmaxf(v, 0.f); v *= v; }
+      if (activation == kActReluSquare) { v = fmaxf(v, 0.f); v *= v; }
       C[(size_t)m * ldc + n] = from_float<T>(v);
     }
   }
@@ -248,7 +352,7 @@ constexpr int GBM = 64, GBN = 128, GBK = 64, GSTAGES = 4;
 __global__ void __launch_bounds__(256)
 expert_linear_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int* __restrict__ order, int top,
                          const __nv_bfloat16* __restrict__ W, __nv_bfloat16* __restrict__ C, int ldc,
-                         const int* __restrict__ offsets, int experts, int N, int K, int relu_square) {
+                         const int* __restrict__ offsets, int experts, int N, int K, int activation, float limit) {
   grid_dependency_wait();
   grid_dependency_launch();
   constexpr int GLD = GBK + 8;          // elements between the rows of a stage
@@ -339,7 +443,11 @@ expert_linear_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int
         const int m = m0 + warp_m * 32 + mi * 16 + (lane >> 2) + half * 8;
         if (m >= end) continue;
         float v0 = acc[mi][ni][2 * half], v1 = acc[mi][ni][2 * half + 1];
-        if (relu_square) {
+        if (activation == kActClampedGlu) {         // (v0, v1) are a feature's gate and up sums
+          C[(size_t)m * ldc + n / 2] = __float2bfloat16_rn(clamped_glu(v0, v1, limit));
+          continue;
+        }
+        if (activation == kActReluSquare) {
           v0 = fmaxf(v0, 0.f);
           v1 = fmaxf(v1, 0.f);
           v0 *= v0;
@@ -351,19 +459,37 @@ expert_linear_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int
 }
 
 // One block per token: out[n, c] = sum_k weights[n, k] * Y[place[n * top + k], c] (+ shared[n, c]), k ascending, float32.
+// With `ids`, a choice whose id is first_identity or more stands for an identity expert: its row is x[n] instead.  With
+// `shared_gate` the shared expert's output is multiplied by sigmoid(shared_gate[n * shared_gate_ld]).
 template <typename T>
 __global__ void expert_combine_kernel(const T* __restrict__ Y, int ldy, const int* __restrict__ place,
                                       const float* __restrict__ weights, int top, const T* __restrict__ shared,
-                                      T* __restrict__ out, int width) {
+                                      T* __restrict__ out, int width, const int* __restrict__ ids, int first_identity,
+                                      const T* __restrict__ x, const float* __restrict__ shared_gate, int shared_gate_ld) {
   grid_dependency_wait();
   grid_dependency_launch();
   const size_t n = blockIdx.x;
+  const float share = shared_gate ? 1.f / (1.f + expf(-shared_gate[n * shared_gate_ld])) : 1.f;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     float sum = 0.f;
-    for (int k = 0; k < top; ++k) sum += weights[n * top + k] * to_float(Y[(size_t)place[n * top + k] * ldy + c]);
-    if (shared) sum += to_float(shared[n * width + c]);
+    for (int k = 0; k < top; ++k) {
+      const bool identity = ids && ids[n * top + k] >= first_identity;
+      const float v = identity ? to_float(x[n * width + c]) : to_float(Y[(size_t)place[n * top + k] * ldy + c]);
+      sum += weights[n * top + k] * v;
+    }
+    if (shared) sum += share * to_float(shared[n * width + c]);
     out[n * width + c] = from_float<T>(sum);
   }
+}
+
+// out[n, j] = clamped_glu(both[n, 2 j], both[n, 2 j + 1])
+template <typename T>
+__global__ void clamped_glu_kernel(const T* __restrict__ both, T* __restrict__ out, size_t total, float limit) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  out[i] = from_float<T>(clamped_glu(to_float(both[2 * i]), to_float(both[2 * i + 1]), limit));
 }
 
 template <typename T>
@@ -385,17 +511,14 @@ using namespace ms;
   else if ((dtype) == MS_BF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
   else MS_FAIL("unknown element type code %d", (dtype));
 
-// x [n_tokens, width]; weight float32 [experts, width]; bias float32 [experts] or null; ids int32 and weights float32
-// [n_tokens, top].
-// x [n_tokens, width]; weight float32 [experts, width]; bias float32 [experts] or null; logits float32 [n_tokens, experts]
-// (scratch, left holding the logits); ids int32 and weights float32 [n_tokens, top].
-MS_EXPORT int ms_router_topk(const void* x, int dtype, const float* weight, const float* bias, int width, int experts,
-                             int top, float* logits, int* ids, float* weights, int n_tokens, cudaStream_t stream) {
-  if (n_tokens == 0) return 0;
-  MS_REQUIRE(experts > 0 && top > 0 && top <= experts, "router_topk: %d of %d experts", top, experts);
-  MS_REQUIRE(dtype == MS_F32 || dtype == MS_BF16, "router_topk: unknown element type code %d", dtype);
+namespace ms {
+
+// Launches the logits kernel: logits[n, e] for the `experts` rows of `weight`.
+static int launch_router_logits(const void* x, int dtype, const float* weight, const float* bias, int width, int experts,
+                                float* logits, int n_tokens, cudaStream_t stream) {
+  MS_REQUIRE(dtype == MS_F32 || dtype == MS_BF16, "router: unknown element type code %d", dtype);
   const size_t element = dtype == MS_F32 ? 4 : 2;
-  MS_REQUIRE((size_t)width * element <= 48 * 1024, "router_topk: a row of %d numbers does not fit the shared memory", width);
+  MS_REQUIRE((size_t)width * element <= 48 * 1024, "router: a row of %d numbers does not fit the shared memory", width);
   int rt = 8;                              // tokens per block: as many rows as 32 KB hold, at most eight
   while (rt > 1 && (size_t)rt * width * element > 32 * 1024) rt >>= 1;
   const int token_tiles = (n_tokens + rt - 1) / rt;
@@ -409,13 +532,47 @@ MS_EXPORT int ms_router_topk(const void* x, int dtype, const float* weight, cons
   if (rt == 8) { MS_ROUTER_LOGITS(8); } else if (rt == 4) { MS_ROUTER_LOGITS(4); } else if (rt == 2) { MS_ROUTER_LOGITS(2); }
   else { MS_ROUTER_LOGITS(1); }
 #undef MS_ROUTER_LOGITS
-  MS_CHECK_LAUNCH("router_topk: logits");
+  MS_CHECK_LAUNCH("router: logits");
+  return 0;
+}
+
+}  // namespace ms
+
+// x [n_tokens, width]; weight float32 [experts, width]; bias float32 [experts] or null; logits float32 [n_tokens, experts]
+// (scratch, left holding the logits); ids int32 and weights float32 [n_tokens, top].
+MS_EXPORT int ms_router_topk(const void* x, int dtype, const float* weight, const float* bias, int width, int experts,
+                             int top, float* logits, int* ids, float* weights, int n_tokens, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  MS_REQUIRE(experts > 0 && top > 0 && top <= experts, "router_topk: %d of %d experts", top, experts);
+  if (launch_router_logits(x, dtype, weight, bias, width, experts, logits, n_tokens, stream)) return 1;
   const int warps = 4;
   const size_t select_smem = (size_t)warps * (experts + top) * sizeof(float);
   MS_REQUIRE(select_smem <= 48 * 1024, "router_topk: %d experts need %zu bytes of shared memory", experts, select_smem);
   ms::launch(router_select_kernel, (n_tokens + warps - 1) / warps, warps * 32, select_smem, stream, (const float*)logits, experts,
              top, ids, weights, n_tokens);
   MS_CHECK_LAUNCH("router_topk: selection");
+  return 0;
+}
+
+// The router whose scores are the softmax over all outputs.  weight float32 [rows, width] with rows >= total: the first
+// `total` rows are the router's outputs, further rows ride along (their logits are left in `logits` for the caller);
+// bias [rows] or null; correction float32 [total] or null; logits float32 [n_tokens, rows]; ids, weights [n_tokens, top].
+MS_EXPORT int ms_router_choose(const void* x, int dtype, const float* weight, const float* bias, int width, int rows,
+                               int total, int top, const float* correction, int group_count, int group_keep, float* logits,
+                               int* ids, float* weights, int n_tokens, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  MS_REQUIRE(total > 0 && rows >= total, "router_choose: %d outputs in %d rows", total, rows);
+  MS_REQUIRE(group_count > 0 && total % group_count == 0 && group_keep >= 1 && group_keep <= group_count,
+             "router_choose: %d outputs in %d groups of which %d are kept", total, group_count, group_keep);
+  MS_REQUIRE(top > 0 && top <= group_keep * (total / group_count), "router_choose: %d of %d outputs (%d of %d groups kept)", top,
+             total, group_keep, group_count);
+  if (launch_router_logits(x, dtype, weight, bias, width, rows, logits, n_tokens, stream)) return 1;
+  const int warps = 4;
+  const size_t smem = (size_t)warps * (2 * total + group_count) * sizeof(float);
+  MS_REQUIRE(smem <= 48 * 1024, "router_choose: %d outputs need %zu bytes of shared memory", total, smem);
+  ms::launch(router_choose_kernel, (n_tokens + warps - 1) / warps, warps * 32, smem, stream, (const float*)logits, rows, total, top,
+             correction, group_count, group_keep, ids, weights, n_tokens);
+  MS_CHECK_LAUNCH("router_choose: selection");
   return 0;
 }
 
@@ -428,14 +585,18 @@ MS_EXPORT int ms_expert_route(const int* ids, int pairs, int experts, int* offse
   return 0;
 }
 
-// A rows of K numbers (row stride lda); order null or [pairs]; W [experts, N, K]; C [pairs, ldc].
+// A rows of K numbers (row stride lda); order null or [pairs]; W [experts, N, K]; C [pairs, ldc].  activation: 0 none,
+// 1 squared ReLU, 2 the clamped gated one (the rows of W alternate gate, up; C then has N / 2 columns).
 MS_EXPORT int ms_expert_linear(const void* A, int dtype, int lda, const int* order, int top, const void* W, void* C, int ldc,
-                               const int* offsets, int experts, int pairs, int N, int K, int relu_square, cudaStream_t stream) {
-  if (pairs == 0 || N == 0) return 0;
+                               const int* offsets, int experts, int pairs, int N, int K, int activation, float limit,
+                               cudaStream_t stream) {
+  if (pairs == 0 || N == 0 || experts == 0) return 0;
   MS_REQUIRE(K > 0 && top > 0, "expert_linear: inner size %d and choices %d must be positive", K, top);
+  MS_REQUIRE(activation >= kActNone && activation <= kActClampedGlu && (activation != kActClampedGlu || N % 2 == 0),
+             "expert_linear: activation %d with %d columns", activation, N);
   const int row_tiles = (pairs + EBM - 1) / EBM + experts;      // every segment may end in a partial tile
   MS_REQUIRE(row_tiles <= 65535, "expert_linear: %d rows in one launch is too many", pairs);
-  if (dtype == MS_BF16 && K % 8 == 0 && N % 8 == 0 && lda % 8 == 0 && ldc % 2 == 0) {
+  if (dtype == MS_BF16 && K % 8 == 0 && N % 8 == 0 && lda % 8 == 0 && (ldc % 2 == 0 || activation == kActClampedGlu)) {
     static_assert(GBM == EBM, "the two kernels walk the same row tiles");
     dim3 mma_grid((N + GBN - 1) / GBN, row_tiles);
     constexpr size_t smem = sizeof(__nv_bfloat16) * GSTAGES * (GBM + GBN) * (GBK + 8);
@@ -446,23 +607,28 @@ MS_EXPORT int ms_expert_linear(const void* A, int dtype, int lda, const int* ord
       allowed = true;
     }
     ms::launch(expert_linear_mma_kernel, mma_grid, 256, smem, stream, (const __nv_bfloat16*)A, lda, order, top,
-               (const __nv_bfloat16*)W, (__nv_bfloat16*)C, ldc, offsets, experts, N, K, relu_square);
+               (const __nv_bfloat16*)W, (__nv_bfloat16*)C, ldc, offsets, experts, N, K, activation, limit);
     MS_CHECK_LAUNCH("expert_linear (tensor cores)");
     return 0;
   }
   dim3 grid((N + EBN - 1) / EBN, row_tiles);
   MS_EXP_DISPATCH(dtype, (ms::launch(expert_linear_kernel<T>, grid, 256, 0, stream, (const T*)A, lda, order, top, (const T*)W,
-                                     (T*)C, ldc, offsets, experts, N, K, relu_square)));
+                                     (T*)C, ldc, offsets, experts, N, K, activation, limit)));
   MS_CHECK_LAUNCH("expert_linear");
   return 0;
 }
 
 // Y [pairs, ldy]; place [n_tokens * top]; weights float32 [n_tokens, top]; shared [n_tokens, width] or null; out [n_tokens, width].
+// ids [n_tokens * top] or null: a choice with ids >= first_identity adds weight * x[token] (x [n_tokens, width]) instead of a
+// row of Y.  shared_gate float32 or null: the logit at shared_gate[token * shared_gate_ld] gates the shared expert's output.
 MS_EXPORT int ms_expert_combine(const void* Y, int dtype, int ldy, const int* place, const float* weights, int top,
-                                const void* shared, void* out, int width, int n_tokens, cudaStream_t stream) {
+                                const void* shared, void* out, int width, int n_tokens, const int* ids, int first_identity,
+                                const void* x, const float* shared_gate, int shared_gate_ld, cudaStream_t stream) {
   if (n_tokens == 0 || width == 0) return 0;
+  MS_REQUIRE(ids == nullptr || x != nullptr, "expert_combine: identity experts need the tokens' rows");
   MS_EXP_DISPATCH(dtype, (ms::launch(expert_combine_kernel<T>, n_tokens, 256, 0, stream, (const T*)Y, ldy, place, weights, top,
-                                     (const T*)shared, (T*)out, width)));
+                                     (const T*)shared, (T*)out, width, ids, first_identity, (const T*)x, shared_gate,
+                                     shared_gate_ld)));
   MS_CHECK_LAUNCH("expert_combine");
   return 0;
 }
@@ -473,5 +639,16 @@ MS_EXPORT int ms_relu_square(void* x, int dtype, long long total, cudaStream_t s
   MS_REQUIRE(blocks < 2147483647LL, "relu_square: %lld elements in one launch is too many", total);
   MS_EXP_DISPATCH(dtype, (ms::launch(relu_square_kernel<T>, (unsigned)blocks, 256, 0, stream, (T*)x, (size_t)total)));
   MS_CHECK_LAUNCH("relu_square");
+  return 0;
+}
+
+// both [n_tokens, 2 * inter] with alternating (gate, up) columns; out [n_tokens, inter].
+MS_EXPORT int ms_clamped_glu(const void* both, int dtype, void* out, int n_tokens, int inter, float limit, cudaStream_t stream) {
+  const long long total = (long long)n_tokens * inter;
+  if (total <= 0) return 0;
+  const long long blocks = (total + 255) / 256;
+  MS_REQUIRE(blocks < 2147483647LL, "clamped_glu: %lld elements in one launch is too many", total);
+  MS_EXP_DISPATCH(dtype, (ms::launch(clamped_glu_kernel<T>, (unsigned)blocks, 256, 0, stream, (const T*)both, (T*)out, (size_t)total, limit)));
+  MS_CHECK_LAUNCH("clamped_glu");
   return 0;
 }

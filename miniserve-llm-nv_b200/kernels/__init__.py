@@ -16,7 +16,7 @@ import torch
 
 from . import build
 
-ABI_VERSION = 7
+ABI_VERSION = 8
 log = logging.getLogger("miniserve_b200")
 _library: Optional[ctypes.CDLL] = None
 
@@ -155,6 +155,63 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
                                 _i(x.numel() // size), _i(size), _f(eps), _stream()))
 
 
+def postnorm_add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor, post_weight: torch.Tensor, post_eps: float,
+                         weight: torch.Tensor, eps: float, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    """``residual += post_weight * delta / rms(delta)`` (float32, in place), ``out = weight * residual / rms(residual)``: a
+    sublayer's output passes a norm of its own on its way into the stream, and the stream is normed for the next
+    sublayer.  With ``rows`` (int32 ``[K]``) only those rows are computed, into ``out [K, H]``, and the residual is left
+    untouched.  The weights may be float32 or bfloat16 whatever ``out`` is."""
+    hidden = residual.shape[1]
+    n_out = residual.shape[0] if rows is None else rows.numel()
+    _want(residual, "residual", torch.float32)
+    _want(delta, "delta", out.dtype, residual.shape)
+    _want(out, "out", None, (n_out, hidden))
+    _want(post_weight, "post_weight", None, (hidden,))
+    _want(weight, "weight", None, (hidden,))
+    if rows is not None:
+        _want(rows, "rows", torch.int32)
+    _check(library().ms_postnorm_add_rmsnorm(_ptr(residual), _ptr(delta), _i(_code(out.dtype)), _ptr(post_weight),
+                                             _i(_code(post_weight.dtype)), _f(post_eps), _ptr(weight), _i(_code(weight.dtype)),
+                                             _f(eps), _ptr(rows), _ptr(out), _i(n_out), _i(hidden), _stream()))
+
+
+def qkv_prepare(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, n_q: int, n_kv: int, head_dim: int, value_dim: int,
+                slots: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                cos_sin: Optional[torch.Tensor], rotary_dim: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                q_out: torch.Tensor) -> None:
+    """Per-head RMSNorm of q and k, half-split rotation of their first ``rotary_dim`` entries, and the append of k and v
+    to one layer's pools, for a projection ``proj [N, ld]`` whose columns are laid out freely: query head h at
+    ``q_col + h * head_dim``, key head g at ``k_col + g * head_dim``, value head g at ``v_col + g * value_dim``.
+    ``k_col < 0``: the projection holds no keys and values (the layer reads another layer's) and only ``q_out
+    [N, n_q, head_dim]`` is written.  Key pool ``[pages, n_kv, page_size, head_dim]``, value pool ``[.., value_dim]``;
+    norm weights float32 ``[head_dim]`` or None; ``cos_sin`` float32 ``[N, rotary_dim / 2, 2]`` or None."""
+    n, ld = proj.shape
+    _want(proj, "proj")
+    _want(q_out, "q_out", proj.dtype, (n, n_q, head_dim))
+    own = k_col >= 0
+    if q_col < 0 or q_col + n_q * head_dim > ld or (own and (k_col + n_kv * head_dim > ld or v_col < 0 or v_col + n_kv * value_dim > ld)):
+        raise KernelError(f"qkv_prepare: columns {q_col}, {k_col}, {v_col} of {n_q}/{n_kv} heads of {head_dim}/{value_dim} in rows of {ld}")
+    if own:
+        _want(slots, "slots", torch.int32, (n,))
+        _want(k_pool, "k_pool", proj.dtype)
+        _want(v_pool, "v_pool", proj.dtype)
+        if (k_pool.dim() != 4 or tuple(k_pool.shape[1:]) != (n_kv, k_pool.shape[2], head_dim)
+                or tuple(v_pool.shape) != tuple(k_pool.shape[:3]) + (value_dim,)):
+            raise KernelError(f"pool shapes {tuple(k_pool.shape)}, {tuple(v_pool.shape)} are not [pages, {n_kv}, page_size, {head_dim} | {value_dim}]")
+    for name, weight in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if weight is not None:
+            _want(weight, name, torch.float32, (head_dim,))
+    if cos_sin is not None:
+        _want(cos_sin, "cos_sin", torch.float32, (n, rotary_dim // 2, 2))
+    else:
+        rotary_dim = 0
+    _check(library().ms_qkv_prepare(
+        _ptr(proj), _i(_code(proj.dtype)), _i(ld), _i(q_col), _i(k_col if own else -1), _i(v_col if own else -1), _i(n_q), _i(n_kv),
+        _i(head_dim), _i(value_dim), _ptr(slots) if own else None, _ptr(q_weight), _ptr(k_weight) if own else None, _f(eps),
+        _ptr(cos_sin), _i(rotary_dim), _ptr(k_pool) if own else None, _ptr(v_pool) if own else None,
+        _i(k_pool.shape[2]), _ptr(q_out), _i(n), _stream()))
+
+
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, cos_sin: torch.Tensor, magnitude: float = 1.0) -> None:
     """``cos_sin[n, j] = magnitude * (cos, sin)(positions[n] * inv_freq[j])`` in float32; cos_sin ``[N, half, 2]``."""
     n, half = positions.numel(), inv_freq.numel()
@@ -238,10 +295,14 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                     request_of_token: torch.Tensor, positions: torch.Tensor, query_start: torch.Tensor,
                     context_lens: torch.Tensor, max_query_len: int, max_context_len: int, scale: float,
                     window: Optional[int], out: torch.Tensor, host_query_start: Optional[list] = None,
-                    softcap: Optional[float] = None, bias_slopes: Optional[torch.Tensor] = None) -> None:
+                    softcap: Optional[float] = None, bias_slopes: Optional[torch.Tensor] = None, sink: bool = False,
+                    gate: Optional[torch.Tensor] = None, gate_col: int = 0) -> None:
     """Causal grouped-query attention of every token over its request's paged keys and values.
 
-    q, out ``[N, n_q, d]``; pools of one layer ``[pages, n_kv, page_size, d]``; block_tables
+    q ``[N, n_q, d]``, out ``[N, n_q, dv]`` (dv: the value pool's last dimension, usually d); pools of one layer
+    ``[pages, n_kv, page_size, d | dv]``.  ``sink``: the softmax's denominator gets one more term ``exp(0)`` (a key of
+    score 0 without a value).  ``gate [N, ld]`` with ``gate_col``: head h's output is multiplied by
+    ``sigmoid(gate[n, gate_col + h])`` as it is stored.  block_tables
     int32 ``[R, width]``; request_of_token, positions int32 ``[N]``; query_start ``[R + 1]`` and
     context_lens ``[R]`` describe the same batch per request (a request's tokens are the last
     ones of its context).  A token at position p sees keys ``max(0, p - window + 1) .. p`` of
@@ -261,11 +322,20 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     """
     n, n_q, head_dim = q.shape
     _want(q, "q")
-    _want(out, "out", q.dtype, q.shape)
     _want(k_pool, "k_pool", q.dtype)
-    _want(v_pool, "v_pool", q.dtype, k_pool.shape)
     if k_pool.dim() != 4 or k_pool.shape[3] != head_dim:
         raise KernelError(f"pool shape {tuple(k_pool.shape)} is not [pages, n_kv, page_size, {head_dim}]")
+    _want(v_pool, "v_pool", q.dtype)
+    if v_pool.dim() != 4 or v_pool.shape[:3] != k_pool.shape[:3]:
+        raise KernelError(f"value pool {tuple(v_pool.shape)} does not go with key pool {tuple(k_pool.shape)}")
+    value_dim = v_pool.shape[3]
+    _want(out, "out", q.dtype, (n, n_q, value_dim))
+    gate_ptr, gate_ld = None, 0
+    if gate is not None:
+        _want(gate, "gate", q.dtype)
+        if gate.dim() != 2 or gate.shape[0] != n or gate_col < 0 or gate_col + n_q > gate.shape[1]:
+            raise KernelError(f"paged_attention: gate logits {tuple(gate.shape)} for {n} tokens of {n_q} heads from column {gate_col}")
+        gate_ptr, gate_ld = gate.data_ptr() + gate_col * gate.element_size(), gate.shape[1]
     _want(block_tables, "block_tables", torch.int32)
     _want(request_of_token, "request_of_token", torch.int32, (n,))
     _want(positions, "positions", torch.int32, (n,))
@@ -277,12 +347,13 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     modified = bool(softcap) or bias_slopes is not None
     if bias_slopes is not None:
         _want(bias_slopes, "bias_slopes", torch.float32, (n_q,))
-    if modified or q.dtype != torch.bfloat16 or not lib.ms_attention_mma_supports(_i(head_dim)):
+    general = modified or sink or gate is not None or value_dim != head_dim
+    if general or q.dtype != torch.bfloat16 or not lib.ms_attention_mma_supports(_i(head_dim)):
         _check(lib.ms_paged_attention_generic(
             _ptr(q), _i(_code(q.dtype)), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _i(block_tables.shape[1]),
             _ptr(request_of_token), _ptr(positions), _i(k_pool.shape[2]), _i(n_q), _i(n_kv), _i(head_dim),
             _f(scale), _i(window if window else 0), _f(softcap if softcap else 0.0), _ptr(bias_slopes), _ptr(out),
-            _i(n), _stream()))
+            _i(n), _i(value_dim), _i(1 if sink else 0), gate_ptr, _i(gate_ld), _stream()))
         return
 
     def run(first: int, last: int, longest: int, rows: int) -> None:
@@ -503,17 +574,125 @@ def linear_batched(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> 
     torch.bmm(x, weight.transpose(1, 2), out=out)
 
 
+# --------------------------------------------------------------------------- state-space mixer
+
+MAX_SCAN_STATE = 256     # numbers of state per channel that selective_scan keeps in registers (8 lanes x 32)
+MAX_CONV_TAPS = 8
+
+
+def _state_rows(states: torch.Tensor, offset: int, length: int) -> int:
+    _want(states, "states", torch.float32)
+    if states.dim() != 2 or offset < 0 or offset + length > states.shape[1]:
+        raise KernelError(f"states {tuple(states.shape)} do not hold {length} numbers from column {offset} per slot")
+    return states.shape[1]
+
+
+def causal_conv_silu(proj: torch.Tensor, col: int, weight: torch.Tensor, bias: torch.Tensor, states: torch.Tensor,
+                     state_offset: int, state_slots: torch.Tensor, query_start: torch.Tensor, max_query_len: int,
+                     out: torch.Tensor) -> None:
+    """Causal convolution per channel, then SiLU, over each request's tokens, continued from the request's state:
+    ``out[t, c] = silu(bias[c] + sum_k weight[c, k] * u[t - (taps - 1 - k), c])`` with ``u`` the columns ``col ..
+    col + channels`` of ``proj [N, ld]``; inputs before the portion come from ``states[slot, state_offset:]`` (float32
+    ``[taps - 1, channels]``, oldest first), which afterwards holds the last ``taps - 1`` inputs seen.  ``weight``
+    float32 ``[channels, taps]``, ``bias`` float32 ``[channels]``; ``state_slots`` int32 ``[R]``, ``query_start`` int32
+    ``[R + 1]``; ``out`` float32 ``[N, channels]``."""
+    n, ld = proj.shape
+    channels, taps = weight.shape
+    _want(proj, "proj")
+    _want(weight, "weight", torch.float32)
+    _want(bias, "bias", torch.float32, (channels,))
+    _want(out, "out", torch.float32, (n, channels))
+    n_requests = state_slots.numel()
+    _want(state_slots, "state_slots", torch.int32)
+    _want(query_start, "query_start", torch.int32, (n_requests + 1,))
+    if col < 0 or col + channels > ld or not 1 <= taps <= MAX_CONV_TAPS:
+        raise KernelError(f"causal_conv_silu: {channels} channels from column {col} of rows of {ld}, {taps} taps")
+    stride = _state_rows(states, state_offset, (taps - 1) * channels)
+    _check(library().ms_causal_conv_silu(_ptr(proj), _i(_code(proj.dtype)), _i(ld), _i(col), _i(channels), _i(taps), _ptr(weight),
+                                         _ptr(bias), _ptr(states), stride, _i(state_offset), _ptr(state_slots), _ptr(query_start),
+                                         _i(n_requests), _i(max_query_len), _ptr(out), _stream()))
+
+
+def selective_scan(conv: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
+                   d: torch.Tensor, states: torch.Tensor, state_offset: int, state_slots: torch.Tensor,
+                   query_start: torch.Tensor, heads: int, head_dim: int, state: int, groups: int, y: torch.Tensor) -> None:
+    """The selective recurrence over each request's tokens, from and into the request's state.  ``conv`` float32
+    ``[N, heads * head_dim + 2 * groups * state]`` = ``[x | B | C]``; the step size of head h is ``softplus(proj[t,
+    dt_col + h] + dt_bias[h])``; per head (group ``h // (heads / groups)``) ``S = exp(-exp(a_log) dt) S + dt B x^T`` and
+    ``y = S^T C + d x``.  ``states[slot, state_offset:]`` holds float32 ``[heads, head_dim, state]``.  ``y`` float32
+    ``[N, heads * head_dim]``."""
+    n, ld = proj.shape
+    inner = heads * head_dim
+    _want(proj, "proj")
+    _want(conv, "conv", torch.float32, (n, inner + 2 * groups * state))
+    for name, tensor in (("dt_bias", dt_bias), ("a_log", a_log), ("d", d)):
+        _want(tensor, name, torch.float32, (heads,))
+    _want(y, "y", torch.float32, (n, inner))
+    n_requests = state_slots.numel()
+    _want(state_slots, "state_slots", torch.int32)
+    _want(query_start, "query_start", torch.int32, (n_requests + 1,))
+    if dt_col < 0 or dt_col + heads > ld or heads % groups or state > MAX_SCAN_STATE:
+        raise KernelError(f"selective_scan: {heads} heads in {groups} groups, state {state}, dt from column {dt_col} of rows of {ld}")
+    stride = _state_rows(states, state_offset, inner * state)
+    _check(library().ms_selective_scan(_ptr(conv), _i(conv.shape[1]), _ptr(proj), _i(_code(proj.dtype)), _i(ld), _i(dt_col),
+                                       _ptr(dt_bias), _ptr(a_log), _ptr(d), _ptr(states), stride, _i(state_offset),
+                                       _ptr(state_slots), _ptr(query_start), _i(n_requests), _i(heads), _i(head_dim), _i(state),
+                                       _i(groups), _ptr(y), _stream()))
+
+
+def gated_group_norm(y: torch.Tensor, proj: torch.Tensor, z_col: int, weight: torch.Tensor, groups: int, eps: float,
+                     out: torch.Tensor) -> None:
+    """``v = y * silu(z)`` with ``z`` the columns ``z_col .. z_col + inner`` of ``proj``; ``out = weight * v / rms(v)``,
+    the root mean square taken over each of ``groups`` equal parts of a row.  ``y`` float32 ``[N, inner]``, ``weight``
+    float32 ``[inner]``, ``out [N, inner]`` in ``proj``'s type."""
+    n, inner = y.shape
+    _want(y, "y", torch.float32)
+    _want(proj, "proj")
+    _want(weight, "weight", torch.float32, (inner,))
+    _want(out, "out", proj.dtype, (n, inner))
+    if proj.shape[0] != n or z_col < 0 or z_col + inner > proj.shape[1] or groups < 1 or inner % groups:
+        raise KernelError(f"gated_group_norm: {inner} channels in {groups} groups, z from column {z_col} of {tuple(proj.shape)}")
+    _check(library().ms_gated_group_norm(_ptr(y), _ptr(proj), _i(_code(proj.dtype)), _i(proj.shape[1]), _i(z_col), _ptr(weight),
+                                         _i(groups), _i(inner), _f(eps), _ptr(out), _i(n), _stream()))
+
+
 # --------------------------------------------------------------------------- routed experts
 
 
 def router_topk(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], top: int, ids: torch.Tensor,
-                weights: torch.Tensor, logits: Optional[torch.Tensor] = None) -> None:
+                weights: torch.Tensor, logits: Optional[torch.Tensor] = None, *, choose_from: Optional[int] = None,
+                scoring: str = "chosen_softmax", correction: Optional[torch.Tensor] = None, groups: tuple = (1, 1)) -> None:
     """Router of a mixture of experts: float32 logits ``x @ weight^T + bias`` (``weight`` float32 ``[E, width]``), the
     ``top`` experts with the largest logits into ``ids`` int32 ``[N, top]`` (ties: the lower index) and the softmax over
     those logits alone into ``weights`` float32 ``[N, top]``.  ``logits`` float32 ``[N, E]``: scratch that is left holding
-    the logits (allocated here if not given)."""
+    the logits (allocated here if not given).
+
+    ``scoring="all_softmax"``: scores are the softmax over the first ``choose_from`` logits of a row (all, if None;
+    further rows of ``weight`` only ride along in the product and leave their logits in ``logits``); the choice goes by
+    ``score + correction`` (float32 ``[choose_from]`` or None) among the members of the ``groups[1]`` best of
+    ``groups[0]`` equal groups of neighbours (a group's score: its largest choice score), and ``weights`` are the chosen
+    outputs' scores as they are."""
     n, width = x.shape
     experts = weight.shape[0]
+    if scoring == "all_softmax":
+        total = experts if choose_from is None else choose_from
+        if logits is None:
+            logits = torch.empty((n, experts), dtype=torch.float32, device=x.device)
+        _want(logits, "logits", torch.float32, (n, experts))
+        _want(x, "x")
+        _want(weight, "weight", torch.float32, (experts, width))
+        if bias is not None:
+            _want(bias, "bias", torch.float32, (experts,))
+        if correction is not None:
+            _want(correction, "correction", torch.float32, (total,))
+        _want(ids, "ids", torch.int32, (n, top))
+        _want(weights, "weights", torch.float32, (n, top))
+        _check(library().ms_router_choose(_ptr(x), _i(_code(x.dtype)), _ptr(weight), _ptr(bias), _i(width), _i(experts), _i(total),
+                                          _i(top), _ptr(correction), _i(groups[0]), _i(groups[1]), _ptr(logits), _ptr(ids),
+                                          _ptr(weights), _i(n), _stream()))
+        return
+    if scoring != "chosen_softmax" or correction is not None or tuple(groups) != (1, 1) or choose_from not in (None, experts):
+        raise KernelError("router_topk: a correction, groups and rows that ride along need scoring='all_softmax'")
     if logits is None:
         logits = torch.empty((n, experts), dtype=torch.float32, device=x.device)
     _want(logits, "logits", torch.float32, (n, experts))
@@ -538,29 +717,45 @@ def expert_route(ids: torch.Tensor, experts: int, offsets: torch.Tensor, order: 
     _check(library().ms_expert_route(_ptr(ids), _i(pairs), _i(experts), _ptr(offsets), _ptr(order), _ptr(place), _stream()))
 
 
+EXPERT_ACTIVATIONS = {"none": 0, "relu_square": 1, "clamped_glu": 2}
+
+
 def expert_linear(x: torch.Tensor, order: Optional[torch.Tensor], top: int, weight: torch.Tensor, out: torch.Tensor,
-                  offsets: torch.Tensor, relu_square: bool = False) -> None:
+                  offsets: torch.Tensor, relu_square: bool = False, activation: str = "none", limit: float = 0.0) -> None:
     """One product per expert over its segment of the sorted pairs: ``out[i] = act(x[src(i)] @ weight[e]^T)`` for every
     place ``i`` of expert ``e``'s segment, ``weight [E, N, K]``, ``out [pairs, N]``.  With ``order`` the rows are gathered from
     the tokens (``src(i) = order[i] // top``, ``x [tokens, K]``), without it ``x [pairs, K]`` is in sorted order already.
-    ``relu_square``: ``act(z) = max(z, 0)^2``."""
+    ``activation``: ``"relu_square"`` (or ``relu_square=True``): ``act(z) = max(z, 0)^2``; ``"clamped_glu"``: the rows of
+    ``weight[e]`` alternate (gate row j, up row j) and ``out [pairs, N / 2]`` receives ``g sigmoid(1.702 g) (u + 1)`` with
+    ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``.  ``offsets`` may bound more segments than ``weight`` has
+    experts (identity experts, sorted behind the others): their rows are left alone."""
     experts, n, k = weight.shape
     pairs = out.shape[0]
+    if relu_square:
+        activation = "relu_square"
+    code = EXPERT_ACTIVATIONS[activation]
     _want(x, "x", None)
     _want(weight, "weight", x.dtype)
-    _want(out, "out", x.dtype, (pairs, n))
-    _want(offsets, "offsets", torch.int32, (experts + 1,))
+    _want(out, "out", x.dtype, (pairs, n // 2 if code == 2 else n))
+    _want(offsets, "offsets", torch.int32)
+    if offsets.numel() < experts + 1:
+        raise KernelError(f"expert_linear: {offsets.numel()} offsets for {experts} experts")
     if x.shape[1] != k or (order is None and x.shape[0] != pairs):
         raise KernelError(f"expert_linear: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
     if order is not None:
         _want(order, "order", torch.int32, (pairs,))
-    _check(library().ms_expert_linear(_ptr(x), _i(_code(x.dtype)), _i(k), _ptr(order), _i(top), _ptr(weight), _ptr(out), _i(n),
-                                      _ptr(offsets), _i(experts), _i(pairs), _i(n), _i(k), _i(1 if relu_square else 0), _stream()))
+    _check(library().ms_expert_linear(_ptr(x), _i(_code(x.dtype)), _i(k), _ptr(order), _i(top), _ptr(weight), _ptr(out),
+                                      _i(out.shape[1]), _ptr(offsets), _i(experts), _i(pairs), _i(n), _i(k), _i(code), _f(limit),
+                                      _stream()))
 
 
 def expert_combine(y: torch.Tensor, place: torch.Tensor, weights: torch.Tensor, shared: Optional[torch.Tensor],
-                   out: torch.Tensor) -> None:
-    """``out[n] = sum_k weights[n, k] * y[place[n * top + k]] (+ shared[n])``, summed in float32 in the order of k."""
+                   out: torch.Tensor, ids: Optional[torch.Tensor] = None, first_identity: int = 0,
+                   x: Optional[torch.Tensor] = None, shared_gate: Optional[torch.Tensor] = None, shared_gate_col: int = 0) -> None:
+    """``out[n] = sum_k weights[n, k] * y[place[n * top + k]] (+ shared[n])``, summed in float32 in the order of k.
+    With ``ids`` (int32 ``[N, top]``) a choice whose id is ``first_identity`` or more is an identity expert and adds
+    ``weights[n, k] * x[n]`` instead.  With ``shared_gate`` (float32 ``[N, ld]``) the shared expert's output is multiplied
+    by ``sigmoid(shared_gate[n, shared_gate_col])``."""
     n, top = weights.shape
     width = out.shape[1]
     _want(y, "y", out.dtype, (n * top, width))
@@ -569,8 +764,27 @@ def expert_combine(y: torch.Tensor, place: torch.Tensor, weights: torch.Tensor, 
     _want(out, "out", None, (n, width))
     if shared is not None:
         _want(shared, "shared", out.dtype, (n, width))
+    gate_ptr, gate_ld = None, 0
+    if ids is not None:
+        _want(ids, "ids", torch.int32, (n, top))
+        _want(x, "x", out.dtype, (n, width))
+    if shared_gate is not None:
+        _want(shared_gate, "shared_gate", torch.float32)
+        if shared_gate.dim() != 2 or shared_gate.shape[0] != n or not 0 <= shared_gate_col < shared_gate.shape[1]:
+            raise KernelError(f"expert_combine: gate logits {tuple(shared_gate.shape)}, column {shared_gate_col}, for {n} tokens")
+        gate_ptr, gate_ld = shared_gate.data_ptr() + 4 * shared_gate_col, shared_gate.shape[1]
     _check(library().ms_expert_combine(_ptr(y), _i(_code(out.dtype)), _i(width), _ptr(place), _ptr(weights), _i(top), _ptr(shared),
-                                       _ptr(out), _i(width), _i(n), _stream()))
+                                       _ptr(out), _i(width), _i(n), _ptr(ids), _i(first_identity),
+                                       _ptr(x) if ids is not None else None, gate_ptr, _i(gate_ld), _stream()))
+
+
+def clamped_glu(both: torch.Tensor, limit: float, out: torch.Tensor) -> None:
+    """``out[n, j] = g sigmoid(1.702 g) (u + 1)`` with ``g = min(both[n, 2 j], limit)`` and ``u = clamp(both[n, 2 j + 1],
+    -limit, limit)``: the gated activation of a product whose weight alternates gate and up rows."""
+    n, inter = out.shape
+    _want(both, "both", None, (n, 2 * inter))
+    _want(out, "out", both.dtype)
+    _check(library().ms_clamped_glu(_ptr(both), _i(_code(both.dtype)), _ptr(out), _i(n), _i(inter), _f(limit), _stream()))
 
 
 def relu_square(x: torch.Tensor) -> None:

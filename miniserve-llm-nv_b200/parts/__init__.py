@@ -1,7 +1,7 @@
 """Layer parts and the model assembled from them."""
 
-from . import attention, block, experts, feed_forward, latent_attention, norm, position  # noqa: F401  (register the built-in parts)
-from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, PAGED_NEEDS, POSITIONS, FoldedInput, NormFold, PagedKVNeed, PagedLatentNeed,
+from . import attention, block, experts, feed_forward, latent_attention, norm, position, state_space  # noqa: F401  (register the built-in parts)
+from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, PAGED_NEEDS, POSITIONS, FoldedInput, NormFold, PagedKVNeed, PagedLatentNeed, PostNormed,
                    ResidualAdd, ParamSpec, Part, StateNeed,
                    register_block, register_feed_forward, register_mixer, register_norm, register_position)
 from .context import PagedKVView, PagedLatentView, StateView, StepContext
@@ -9,6 +9,6 @@ from .model import CacheGroup, DecoderModel, RunCache
 from .spec import LayerRun, LayerSpec, ModelSpec, PartSpec
 
 __all__ = ["BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "PAGED_NEEDS", "POSITIONS", "FoldedInput", "NormFold", "PagedKVNeed",
-           "PagedLatentNeed", "PagedLatentView", "ResidualAdd", "ParamSpec", "Part", "StateNeed", "register_block", "register_feed_forward", "register_mixer", "register_norm",
+           "PagedLatentNeed", "PagedLatentView", "PostNormed", "ResidualAdd", "ParamSpec", "Part", "StateNeed", "register_block", "register_feed_forward", "register_mixer", "register_norm",
            "register_position", "PagedKVView", "StateView", "StepContext", "CacheGroup", "DecoderModel", "RunCache",
            "LayerRun", "LayerSpec", "ModelSpec", "PartSpec"]

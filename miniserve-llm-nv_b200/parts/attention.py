@@ -14,6 +14,16 @@ overrides the score scale; ``position`` is a :class:`~.spec.PartSpec` of the pos
 number per query head) adds ``slope * (key position - query position)`` to it: position
 encodings that act on the scores instead of on queries and keys.  Either of them selects the
 general attention kernel.
+
+Further options, each off by default: ``value_dim`` (value heads of another size than query and key heads; the
+output projection then reads ``num_heads * value_dim`` numbers), ``sink`` (the softmax's denominator gets one more
+term, ``exp(0)``: a key of score 0 that has no value, so a head can attend to nothing), ``output_gate`` (head h's
+output is multiplied by ``sigmoid(W_g x)_h``, one number per head, from the same input as the projections) and
+``own_kv=False`` (the layer has no key and value tensors: its run reads another run's cache, ``LayerRun.cache_of``,
+with its own queries).  With any of them the projections (queries, keys and values if the layer has them, gate
+logits) are one product over a row-concatenated weight padded with zero rows to a multiple of eight, followed by
+``kernels.qkv_prepare`` (per-head norm, rotation, append) and ``kernels.paged_attention`` with the sink and the gate
+applied as it stores.
 """
 
 from __future__ import annotations
@@ -36,7 +46,8 @@ class Attention(Part):
                  score_bias_slopes: Optional[Sequence[float]] = None,
                  q_name: str = "q_proj.weight", k_name: str = "k_proj.weight",
                  v_name: str = "v_proj.weight", o_name: str = "o_proj.weight", q_norm_name: str = "q_norm.weight",
-                 k_norm_name: str = "k_norm.weight") -> None:
+                 k_norm_name: str = "k_norm.weight", value_dim: Optional[int] = None, sink: bool = False,
+                 output_gate: bool = False, own_kv: bool = True, gate_name: str = "g_proj.weight") -> None:
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} key/value heads")
         if head_dim % 2 or not 2 <= head_dim <= kernels.MAX_HEAD_DIM:
@@ -55,8 +66,26 @@ class Attention(Part):
         self._slopes_on_device: Optional[torch.Tensor] = None
         self.position = POSITIONS.build(position, head_dim=head_dim) if "head_dim" not in position.args \
             else POSITIONS.build(position)
+        self.value_dim = head_dim if value_dim is None else int(value_dim)
+        if not 1 <= self.value_dim <= kernels.MAX_HEAD_DIM:
+            raise ValueError(f"value head size {self.value_dim} is not in 1..{kernels.MAX_HEAD_DIM}")
+        self.sink, self.output_gate, self.own_kv = bool(sink), bool(output_gate), bool(own_kv)
+        # the general form: one product for all projections of the input, then qkv_prepare and the general call of
+        # paged_attention (the fast paths below are written for plain heads of one size)
+        self.general = self.sink or self.output_gate or not self.own_kv or self.value_dim != head_dim
+        if self.general and (self.score_softcap or self.score_bias_slopes is not None):
+            raise ValueError("score modifiers are not implemented together with value_dim, sink, output_gate or own_kv=False")
+        if self.general and getattr(self.position, "interleaved", False):
+            raise ValueError("value_dim, sink, output_gate and own_kv=False are implemented for the half-split rotation")
         self.names = dict(q=prefix + q_name, k=prefix + k_name, v=prefix + v_name, o=prefix + o_name,
-                          q_norm=prefix + q_norm_name, k_norm=prefix + k_norm_name)
+                          q_norm=prefix + q_norm_name, k_norm=prefix + k_norm_name, g=prefix + gate_name)
+        # columns of the general form's projection: queries, keys, values, gate logits, zero padding
+        q_rows = num_heads * head_dim
+        kv_rows = num_kv_heads * (head_dim + self.value_dim) if self.own_kv else 0
+        self.k_col = q_rows if self.own_kv else -1
+        self.v_col = q_rows + num_kv_heads * head_dim if self.own_kv else -1
+        self.gate_col = q_rows + kv_rows if self.output_gate else -1
+        self.in_rows = (q_rows + kv_rows + (num_heads if self.output_gate else 0) + 7) // 8 * 8
         self.qkv_weight: Optional[torch.Tensor] = None
         self.o_weight: Optional[torch.Tensor] = None
         self.q_norm_weight: Optional[torch.Tensor] = None
@@ -64,22 +93,38 @@ class Attention(Part):
 
     # ------------------------------------------------------------------ declaration
     def param_specs(self) -> list[ParamSpec]:
-        h, d = self.hidden_size, self.head_dim
-        specs = [ParamSpec(self.names["q"], (self.num_heads * d, h)),
-                 ParamSpec(self.names["k"], (self.num_kv_heads * d, h)),
-                 ParamSpec(self.names["v"], (self.num_kv_heads * d, h)),
-                 ParamSpec(self.names["o"], (h, self.num_heads * d))]
+        h, d, dv = self.hidden_size, self.head_dim, self.value_dim
+        specs = [ParamSpec(self.names["q"], (self.num_heads * d, h))]
+        if self.own_kv:
+            specs += [ParamSpec(self.names["k"], (self.num_kv_heads * d, h)), ParamSpec(self.names["v"], (self.num_kv_heads * dv, h))]
         if self.qk_norm:
-            specs += [ParamSpec(self.names["q_norm"], (d,), "vector"), ParamSpec(self.names["k_norm"], (d,), "vector")]
+            specs.append(ParamSpec(self.names["q_norm"], (d,), "vector"))
+            if self.own_kv:
+                specs.append(ParamSpec(self.names["k_norm"], (d,), "vector"))
+        if self.output_gate:
+            specs.append(ParamSpec(self.names["g"], (self.num_heads, h)))
+        specs.append(ParamSpec(self.names["o"], (h, self.num_heads * dv)))
         return specs
 
     def cache_need(self) -> PagedKVNeed:
-        return PagedKVNeed(self.num_kv_heads, self.head_dim, self.window)
+        return PagedKVNeed(self.num_kv_heads, self.head_dim, self.window, None if self.value_dim == self.head_dim else self.value_dim)
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
         n = self.names
-        self.qkv_weight = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]], dim=0).contiguous()
         self.o_weight = tensors[n["o"]]
+        if self.general:
+            pieces = [tensors[n["q"]]] + ([tensors[n["k"]], tensors[n["v"]]] if self.own_kv else [])
+            if self.output_gate:
+                pieces.append(tensors[n["g"]])
+            padding = self.in_rows - sum(p.shape[0] for p in pieces)
+            if padding:
+                pieces.append(torch.zeros((padding, self.hidden_size), dtype=pieces[0].dtype, device=pieces[0].device))
+            self.qkv_weight = torch.cat(pieces, dim=0).contiguous()
+            if self.qk_norm:
+                self.q_norm_weight = tensors[n["q_norm"]].float().contiguous()
+                self.k_norm_weight = tensors[n["k_norm"]].float().contiguous() if self.own_kv else None
+            return
+        self.qkv_weight = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]], dim=0).contiguous()
         if self.qk_norm:
             self.q_norm_weight, self.k_norm_weight = tensors[n["q_norm"]], tensors[n["k_norm"]]
             if self.q_norm_weight.dtype != self.k_norm_weight.dtype:
@@ -88,16 +133,18 @@ class Attention(Part):
 
     # ------------------------------------------------------------------ norms folded into the projections
     def fold_input_weight(self, ctx: StepContext) -> Optional[torch.Tensor]:
-        return self.qkv_weight
+        return None if self.general else self.qkv_weight
 
     def fold_output_weight(self, ctx: StepContext) -> Optional[torch.Tensor]:
-        return self.o_weight
+        return None if self.general else self.o_weight
 
     # ------------------------------------------------------------------ work
     def forward(self, x, ctx: StepContext, cache: PagedKVView, fold: Union[None, NormFold, ResidualAdd] = None):
         """``x``: the normed input, or a :class:`FoldedInput`.  With a :class:`NormFold` the output projection adds
         into the residual stream and a :class:`FoldedInput` for the part behind the following norm is returned;
         with a :class:`ResidualAdd` it adds into the stream and nothing is returned."""
+        if self.general:
+            return self._forward_general(x, ctx, cache)
         stats = None
         if isinstance(x, FoldedInput):
             x, stats = x.x, x.stats
@@ -141,6 +188,27 @@ class Attention(Part):
                                                  fold.eps, out, partials)
             return FoldedInput(out, stats)
         kernels.linear(attended.view(n, n_q * d), self.o_weight, out)
+        return out
+
+    def _forward_general(self, x: torch.Tensor, ctx: StepContext, cache: PagedKVView) -> torch.Tensor:
+        """The form with a sink, a gate, value heads of their own size or another run's keys and values."""
+        n, d, dv = x.shape[0], self.head_dim, self.value_dim
+        n_q, n_kv = self.num_heads, self.num_kv_heads
+        if cache.writable != self.own_kv:
+            raise RuntimeError("a layer with keys and values of its own writes its cache; a layer without reads another run's")
+        proj = ctx.buffer("attention.proj", (n, self.in_rows), x.dtype)
+        kernels.linear(x, self.qkv_weight, proj)
+        cos_sin, rotary_dim, _ = self.position.fused_args(ctx)
+        q = ctx.buffer("attention.q", (n, n_q, d), x.dtype)
+        kernels.qkv_prepare(proj, 0, self.k_col, self.v_col, n_q, n_kv, d, dv, cache.slots, self.q_norm_weight,
+                            self.k_norm_weight, self.eps, cos_sin, rotary_dim, cache.key_pool, cache.value_pool, q)
+        attended = ctx.buffer("attention.attended", (n, n_q, dv), x.dtype)
+        kernels.paged_attention(q, cache.key_pool, cache.value_pool, cache.block_tables, ctx.request_of_token,
+                                ctx.positions, ctx.query_start, ctx.context_lens, ctx.max_query_len,
+                                ctx.max_context_len, self.scale, self.window, attended, ctx.host_query_start or None,
+                                sink=self.sink, gate=proj if self.output_gate else None, gate_col=max(self.gate_col, 0))
+        out = ctx.buffer("attention.out", (n, self.hidden_size), x.dtype)
+        kernels.linear(attended.view(n, n_q * dv), self.o_weight, out)
         return out
 
     def _attend(self, q: torch.Tensor, ctx: StepContext, cache: PagedKVView, attended: torch.Tensor) -> None:

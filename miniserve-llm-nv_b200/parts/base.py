@@ -54,11 +54,17 @@ class ParamSpec:
 
 @dataclass(frozen=True)
 class PagedKVNeed:
-    """The mixer keeps keys and values per token in pages; ``window`` keys back at most (None: all)."""
+    """The mixer keeps keys and values per token in pages; ``window`` keys back at most (None: all).  ``value_dim``:
+    the size of a value head where it differs from the size of a key head (None: the same)."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_dim: Optional[int] = None
+
+    @property
+    def value_head_dim(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
 
 @dataclass(frozen=True)
@@ -101,6 +107,18 @@ class ResidualAdd:
     alone instead of adding a separate output into it first."""
 
     residual: torch.Tensor
+
+
+@dataclass
+class PostNormed:
+    """What a block hands on where a sublayer's output passes a norm of its own before it is added to the stream:
+    ``x`` is the output as computed, ``weight`` and ``eps`` are that norm's (``weight * x / rms(x)`` is what the stream
+    receives).  The norm that reads the stream next carries out both in one kernel
+    (``kernels.postnorm_add_rmsnorm``)."""
+
+    x: torch.Tensor
+    weight: torch.Tensor
+    eps: float
 
 
 @dataclass

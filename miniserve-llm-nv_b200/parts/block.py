@@ -1,6 +1,7 @@
 """Block arrangements.  ``pre_norm``: ``h += mixer(norm(h)); h += feed_forward(norm(h))``
 (miniserve/model/qwen3.py:336-346).  ``parallel``: one norm whose output both sublayers read,
 ``h += mixer(norm(h)) + feed_forward(norm(h))``; a layer without a feed-forward is ``h += mixer(norm(h))``.
+``sandwich``: a norm on both sides of each sublayer, ``h += post(mixer(norm(h))); h += post(feed_forward(norm(h)))``.
 
 The residual stream ``h`` is float32 and is updated in place.  A block receives the stream
 together with a *pending* ``delta`` that has not been added yet (the previous block's
@@ -22,11 +23,11 @@ from typing import Any, Optional, Union
 import torch
 
 from .. import kernels
-from .base import FoldedInput, NormFold, ResidualAdd, register_block
+from .base import FoldedInput, NormFold, PostNormed, ResidualAdd, register_block
 from .context import StepContext
 
 # what a block hands on: nothing, an output still to add (or two, whose float32 sum is to be added), or a folded input
-Pending = Union[None, torch.Tensor, tuple, FoldedInput]
+Pending = Union[None, torch.Tensor, tuple, FoldedInput, PostNormed]
 
 
 def fold_between(producer, norm, consumer, ctx: StepContext) -> Optional[tuple]:
@@ -119,3 +120,37 @@ class ParallelBlock:
         if self.feed_forward is None:
             return mixed
         return mixed, self.feed_forward.forward(normed, ctx)
+
+
+@register_block("sandwich")
+class SandwichBlock:
+    """``x <- x + post_1(mixer(norm_1(x)))``, then ``x <- x + post_2(feed_forward(norm_2(x)))``: every sublayer has a
+    norm before it and a norm of its own output.  A layer may have no feed-forward.
+
+    A sublayer's output is handed on unadded together with its output norm (:class:`~.base.PostNormed`); the norm that
+    reads the stream next (this block's second, the next block's first, or the model's last) norms the output, adds it
+    to the float32 stream and norms the stream in one kernel.
+    """
+
+    def __init__(self, *, mixer, feed_forward, mixer_norm, feed_forward_norm, mixer_post_norm, feed_forward_post_norm=None) -> None:
+        if (feed_forward is None) != (feed_forward_norm is None) or (feed_forward is None) != (feed_forward_post_norm is None):
+            raise ValueError("a sandwich block has a feed-forward with both of its norms, or none of the three")
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.mixer_post_norm = mixer_norm, mixer_post_norm
+        self.feed_forward_norm, self.feed_forward_post_norm = feed_forward_norm, feed_forward_post_norm
+
+    def parts(self):
+        every = (self.mixer_norm, self.mixer, self.mixer_post_norm, self.feed_forward_norm, self.feed_forward, self.feed_forward_post_norm)
+        return [part for part in every if part is not None]
+
+    def forward(self, residual: torch.Tensor, pending: Pending, ctx: StepContext, cache: Any) -> Pending:
+        if isinstance(pending, FoldedInput):
+            raise TypeError("a sandwich block takes its input from its own norm")
+        normed = ctx.buffer("block.normed", tuple(residual.shape), ctx.dtype)
+        self.mixer_norm.add_and_norm(residual, pending, normed)
+        mixed = PostNormed(self.mixer.forward(normed, ctx, cache), *self.mixer_post_norm.fold())
+        if self.feed_forward is None:
+            return mixed
+        normed = ctx.buffer("block.normed", tuple(residual.shape), ctx.dtype)      # (the mixer has read the first)
+        self.feed_forward_norm.add_and_norm(residual, mixed, normed)
+        return PostNormed(self.feed_forward.forward(normed, ctx), *self.feed_forward_post_norm.fold())

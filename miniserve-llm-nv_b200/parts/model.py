@@ -42,8 +42,12 @@ class DecoderModel:
             feed_forward = None if layer.feed_forward is None else FEED_FORWARDS.build(layer.feed_forward, prefix=layer.prefix)
             mixer_norm = NORMS.build(layer.mixer_norm, prefix=layer.prefix)
             feed_forward_norm = None if layer.feed_forward_norm is None else NORMS.build(layer.feed_forward_norm, prefix=layer.prefix)
+            post = {}
+            for key, part in (("mixer_post_norm", layer.mixer_post_norm), ("feed_forward_post_norm", layer.feed_forward_post_norm)):
+                if part is not None:
+                    post[key] = NORMS.build(part, prefix=layer.prefix)
             self.blocks.append(BLOCKS.build(layer.block, mixer=mixer, feed_forward=feed_forward,
-                                            mixer_norm=mixer_norm, feed_forward_norm=feed_forward_norm))
+                                            mixer_norm=mixer_norm, feed_forward_norm=feed_forward_norm, **post))
         self.final_norm = NORMS.build(spec.final_norm)
         for index, run in enumerate(spec.order):
             if not 0 <= run.layer < len(self.blocks):

@@ -1,5 +1,6 @@
 """Norm parts.  ``rms``: ``weight * x * rsqrt(mean(x^2) + eps)`` with the statistics in float32
-(miniserve/model/layers.py:30-34), fused with the residual add that precedes it."""
+(miniserve/model/layers.py:30-34), fused with the residual add that precedes it.  ``one_plus``: the stored weight
+lies around zero and stands for ``1 + weight`` (added once, in float32, when the weight is loaded)."""
 
 from __future__ import annotations
 
@@ -8,13 +9,14 @@ from typing import Optional
 import torch
 
 from .. import kernels
-from .base import ParamSpec, Part, register_norm
+from .base import ParamSpec, Part, PostNormed, register_norm
 
 
 @register_norm("rms")
 class RMSNorm(Part):
-    def __init__(self, *, name: str, size: int, eps: float, prefix: str = "") -> None:
+    def __init__(self, *, name: str, size: int, eps: float, prefix: str = "", one_plus: bool = False) -> None:
         self.name, self.size, self.eps = prefix + name, size, float(eps)
+        self.one_plus = bool(one_plus)
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> list[ParamSpec]:
@@ -22,6 +24,8 @@ class RMSNorm(Part):
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
         self.weight = tensors[self.name]
+        if self.one_plus:
+            self.weight = (self.weight.float() + 1.0).contiguous()
 
     def add_and_norm(self, residual: torch.Tensor, delta, out: torch.Tensor,
                      rows: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -32,6 +36,10 @@ class RMSNorm(Part):
         With ``rows`` only those rows are normalised into ``out [len(rows), size]`` and the
         residual stays as it is.
         """
+        if isinstance(delta, PostNormed):
+            # the output of the sublayer before passes its own norm on the way into the stream: one kernel for both
+            kernels.postnorm_add_rmsnorm(residual, delta.x, delta.weight, delta.eps, self.weight, self.eps, out, rows)
+            return out
         second = None
         if isinstance(delta, tuple):
             delta, second = delta

@@ -32,6 +32,9 @@ class LayerSpec:
     mixer_norm: PartSpec
     feed_forward_norm: Optional[PartSpec]      # None: the block has one norm (``parallel``)
     block: PartSpec = PartSpec("pre_norm")
+    # norms of a sublayer's OUTPUT, before it is added to the stream (blocks that norm on both sides of a sublayer)
+    mixer_post_norm: Optional[PartSpec] = None
+    feed_forward_post_norm: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)

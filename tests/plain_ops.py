@@ -140,7 +140,7 @@ def linear_add(x, weight, residual):
 
 def paged_attention(q, k_pool, v_pool, block_tables, request_of_token, positions, query_start, context_lens,
                     max_query_len, max_context_len, scale, window, out, host_query_start=None, softcap=None,
-                    bias_slopes=None):
+                    bias_slopes=None, sink=False, gate=None, gate_col=0):
     n, n_q, d = q.shape
     n_kv, page_size = k_pool.shape[1], k_pool.shape[2]
     group = n_q // n_kv
@@ -159,8 +159,16 @@ def paged_attention(q, k_pool, v_pool, block_tables, request_of_token, positions
                 scores = softcap * torch.tanh(scores / softcap)
             if bias_slopes is not None:
                 scores = scores + float(bias_slopes[head]) * (keys - pos).double()
-            p = torch.softmax(scores, dim=0)
-            out[token, head] = (p @ v[:, head // group, :]).to(out.dtype)
+            if sink:        # one more term exp(0) in the denominator: a key of score 0 without a value
+                top = torch.clamp(scores.max(), min=0.0)
+                e = torch.exp(scores - top)
+                p = e / (e.sum() + torch.exp(-top))
+            else:
+                p = torch.softmax(scores, dim=0)
+            result = p @ v[:, head // group, :]
+            if gate is not None:
+                result = result * torch.sigmoid(gate[token, gate_col + head].double())
+            out[token, head] = result.to(out.dtype)
 
 
 def linear(x, weight, out, row_stats=None):
@@ -246,12 +254,28 @@ def linear_batched(x, weight, out):
 # --------------------------------------------------------------------------- routed experts
 
 
-def router_topk(x, weight, bias, top, ids, weights, scratch=None):
+def router_topk(x, weight, bias, top, ids, weights, scratch=None, *, choose_from=None, scoring="chosen_softmax",
+                correction=None, groups=(1, 1)):
     logits = x.double() @ weight.double().T
     if bias is not None:
         logits = logits + bias.double()
     if scratch is not None:
         scratch.copy_(logits.to(scratch.dtype))
+    if scoring == "all_softmax":
+        total = logits.shape[1] if choose_from is None else choose_from
+        n = logits.shape[0]
+        scores = torch.softmax(logits[:, :total], dim=1)
+        choice = scores if correction is None else scores + correction.double()
+        count, keep = groups
+        if keep < count:
+            best = choice.view(n, count, total // count).max(dim=2).values
+            kept = torch.zeros(n, count, dtype=torch.bool)
+            kept.scatter_(1, best.sort(dim=1, descending=True, stable=True).indices[:, :keep], True)
+            choice = choice.masked_fill(~kept[:, :, None].expand(n, count, total // count).reshape(n, total), -math.inf)
+        chosen = choice.sort(dim=1, descending=True, stable=True).indices[:, :top]
+        ids.copy_(chosen.to(ids.dtype))
+        weights.copy_(torch.gather(scores, 1, chosen).to(weights.dtype))
+        return
     ranked = logits.sort(dim=1, descending=True, stable=True)
     ids.copy_(ranked.indices[:, :top].to(ids.dtype))
     weights.copy_(torch.softmax(ranked.values[:, :top], dim=1).to(weights.dtype))
@@ -267,29 +291,132 @@ def expert_route(ids, experts, offsets, order, place):
     offsets[1:] = counts.cumsum(0).to(offsets.dtype)
 
 
-def expert_linear(x, order, top, weight, out, offsets, relu_square=False):
+def clamped_glu_values(gate, up, limit):
+    g, u = gate.clamp(max=limit), up.clamp(min=-limit, max=limit)
+    return g * torch.sigmoid(1.702 * g) * (u + 1.0)
+
+
+def clamped_glu(both, limit, out):
+    both = both.double()
+    out.copy_(clamped_glu_values(both[:, 0::2], both[:, 1::2], limit).to(out.dtype))
+
+
+def expert_linear(x, order, top, weight, out, offsets, relu_square=False, activation="none", limit=0.0):
     for e in range(weight.shape[0]):
         lo, hi = int(offsets[e]), int(offsets[e + 1])
         if hi == lo:
             continue
         rows = x[(order[lo:hi] // top).long()] if order is not None else x[lo:hi]
         y = rows.double() @ weight[e].double().T
-        if relu_square:
+        if relu_square or activation == "relu_square":
             y = y.clamp(min=0).pow(2)
+        elif activation == "clamped_glu":
+            y = clamped_glu_values(y[:, 0::2], y[:, 1::2], limit)
         out[lo:hi] = y.to(out.dtype)
 
 
-def expert_combine(y, place, weights, shared, out):
+def expert_combine(y, place, weights, shared, out, ids=None, first_identity=0, x=None, shared_gate=None, shared_gate_col=0):
     n, top = weights.shape
     picked = y.double()[place.long()].view(n, top, -1)
+    if ids is not None:
+        identity = (ids.long() >= first_identity)[:, :, None]
+        picked = torch.where(identity, x.double()[:, None, :].expand_as(picked), picked)
     total = (weights.double()[:, :, None] * picked).sum(dim=1)
     if shared is not None:
-        total = total + shared.double()
+        share = shared.double()
+        if shared_gate is not None:
+            share = share * torch.sigmoid(shared_gate[:, shared_gate_col].double())[:, None]
+        total = total + share
     out.copy_(total.to(out.dtype))
 
 
 def relu_square(x):
     x.copy_(x.double().clamp(min=0).pow(2).to(x.dtype))
+
+
+# --------------------------------------------------------------------------- norms on both sides, free projection layouts
+
+
+def postnorm_add_rmsnorm(residual, delta, post_weight, post_eps, weight, eps, out, rows=None):
+    d = delta.double()
+    add = post_weight.double() * (d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + post_eps))
+    if rows is None:
+        residual += add.to(residual.dtype)
+        x = residual.double()
+    else:
+        x = (residual.double() + add)[rows.long()]
+    out.copy_((weight.double() * (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps))).to(out.dtype))
+
+
+def qkv_prepare(proj, q_col, k_col, v_col, n_q, n_kv, head_dim, value_dim, slots, q_weight, k_weight, eps, cos_sin,
+                rotary_dim, k_pool, v_pool, q_out):
+    n = proj.shape[0]
+
+    def heads(col, count, size, weight):
+        x = proj[:, col:col + count * size].double().view(n, count, size)
+        if weight is not None:
+            x = weight.double() * (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps))
+        if cos_sin is not None:
+            x = rotate(x, cos_sin, rotary_dim, False)
+        return x
+
+    q_out.copy_(heads(q_col, n_q, head_dim, q_weight).to(q_out.dtype))
+    if k_col < 0:
+        return
+    k = heads(k_col, n_kv, head_dim, k_weight)
+    v = proj[:, v_col:v_col + n_kv * value_dim].view(n, n_kv, value_dim)
+    page_size = k_pool.shape[2]
+    for token in range(n):
+        slot = int(slots[token])
+        if slot < 0:
+            continue
+        k_pool[slot // page_size, :, slot % page_size, :] = k[token].to(k_pool.dtype)
+        v_pool[slot // page_size, :, slot % page_size, :] = v[token]
+
+
+# --------------------------------------------------------------------------- state-space mixer
+
+
+def causal_conv_silu(proj, col, weight, bias, states, state_offset, state_slots, query_start, max_query_len, out):
+    channels, taps = weight.shape
+    keep = taps - 1
+    for r in range(state_slots.numel()):
+        lo, hi = int(query_start[r]), int(query_start[r + 1])
+        if hi == lo:
+            continue
+        state = states[int(state_slots[r]), state_offset:state_offset + keep * channels].view(keep, channels)
+        u = torch.cat([state.double(), proj[lo:hi, col:col + channels].double()], dim=0)      # inputs -keep .. hi - lo - 1
+        total = bias.double().expand(hi - lo, -1).clone()
+        for k in range(taps):
+            total = total + u[k:k + hi - lo] * weight[:, k].double()
+        out[lo:hi] = (total * torch.sigmoid(total)).to(out.dtype)
+        state.copy_(u[u.shape[0] - keep:].to(state.dtype))
+
+
+def selective_scan(conv, proj, dt_col, dt_bias, a_log, d, states, state_offset, state_slots, query_start, heads, head_dim,
+                   state, groups, y):
+    inner = heads * head_dim
+    for r in range(state_slots.numel()):
+        lo, hi = int(query_start[r]), int(query_start[r + 1])
+        kept = states[int(state_slots[r]), state_offset:state_offset + inner * state].view(heads, head_dim, state)
+        S = kept.double()
+        for t in range(lo, hi):
+            x = conv[t, :inner].double().view(heads, head_dim)
+            B = conv[t, inner:inner + groups * state].double().view(groups, state).repeat_interleave(heads // groups, dim=0)
+            C = conv[t, inner + groups * state:].double().view(groups, state).repeat_interleave(heads // groups, dim=0)
+            step = torch.nn.functional.softplus(proj[t, dt_col:dt_col + heads].double() + dt_bias.double(), threshold=30.0)
+            decay = torch.exp(-torch.exp(a_log.double()) * step)
+            S = decay[:, None, None] * S + (step[:, None] * x)[:, :, None] * B[:, None, :]
+            y[t] = ((S * C[:, None, :]).sum(-1) + d.double()[:, None] * x).reshape(inner).to(y.dtype)
+        kept.copy_(S.to(kept.dtype))
+
+
+def gated_group_norm(y, proj, z_col, weight, groups, eps, out):
+    n, inner = y.shape
+    z = proj[:, z_col:z_col + inner].double()
+    v = (y.double() * z * torch.sigmoid(z)).view(n, groups, inner // groups)
+    v = (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)).reshape(n, inner)
+    out.copy_((v * weight.double()).to(out.dtype))
 
 
 def install(monkeypatch) -> None:
@@ -300,7 +427,8 @@ def install(monkeypatch) -> None:
     for name in ("embedding", "add_rmsnorm", "rmsnorm", "rope_table", "qk_norm_rope_append", "silu_mul",
                  "paged_attention", "linear", "gated_linear", "gated_up", "sample", "scale_softcap", "latent_prepare",
                  "latent_attention", "head_gate", "linear_batched", "router_topk", "expert_route", "expert_linear",
-                 "expert_combine", "relu_square"):
+                 "expert_combine", "relu_square", "clamped_glu", "postnorm_add_rmsnorm", "qkv_prepare", "causal_conv_silu",
+                 "selective_scan", "gated_group_norm"):
         monkeypatch.setattr(kernels, name, globals()[name])
     monkeypatch.setattr(kernels, "attention_kernels", lambda *sizes: {"decode": "plain", "prompt": "plain"})
     monkeypatch.setattr(kernels, "latent_attention_kernels", lambda *sizes: {"decode": "plain", "prompt": "plain"})
