@@ -32,7 +32,7 @@ def build_zozezen_spec(config: ZozezenConfig) -> ModelSpec:
         m = layer.mixer
         cache_of = None
         if layer.type == "attention":
-            position = PartSpec("rope", dict(head_dim=m.dim, theta=m.rot.base, rotary_dim=m.rot.dims))
+            position = PartSpec("rope", dict(head_dim=m.dim, theta=m.rot.base, rotary_dim=m.rot.dims, frequencies="float64"))
             mixer = PartSpec("attention", dict(
                 hidden_size=width, num_heads=m.heads, num_kv_heads=m.kv_heads, head_dim=m.dim, value_dim=m.vdim, qk_norm=True,
                 eps=eps, position=position, scale=m.scale, sink=True, output_gate=True, own_kv=m.kv_from is None,

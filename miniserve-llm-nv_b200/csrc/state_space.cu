@@ -47,8 +47,9 @@ causal_conv_silu_kernel(const T* __restrict__ proj, int ld, int col, int channel
   // inputs before token t0: from the batch where the request's portion reaches back that far, else from the state
   // (the input at local index i < 0 is state[keep + i])
 #pragma unroll
-  for (int k = 0; k < kMaxTaps; ++k) {
-    window[k] = 0.f;
+  for (int k = 0; k < kMaxTaps; ++k) window[k] = 0.f;
+#pragma unroll
+  for (int k = 0; k + 1 < kMaxTaps; ++k) {
     if (k + 1 < taps) {                      // slots 1 .. taps - 1 hold inputs t0 - keep + k .. ; slot 0 is shifted out first
       const int i = t0 - keep + k;
       window[k + 1] = i >= 0 ? to_float(proj[(size_t)(q0 + i) * ld + col + c]) : state[(size_t)(keep + i) * channels + c];

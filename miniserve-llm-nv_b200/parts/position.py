@@ -51,7 +51,8 @@ def scaled_frequencies(dims: int, theta: float, factor: float, original: float, 
 @register_position("rope")
 class RotaryPosition(Part):
     def __init__(self, *, head_dim: int, theta: float, rotary_dim: Optional[int] = None,
-                 interleaved: bool = False, scaling: Optional[Mapping[str, float]] = None) -> None:
+                 interleaved: bool = False, scaling: Optional[Mapping[str, float]] = None,
+                 frequencies: str = "float32") -> None:
         self.head_dim = head_dim
         self.theta = float(theta)
         self.rotary_dim = head_dim if rotary_dim is None else rotary_dim
@@ -60,6 +61,11 @@ class RotaryPosition(Part):
             raise ValueError(f"rotary size {self.rotary_dim} must be even and within the head size {head_dim}")
         # ``scaling``: the mapping {factor, original, fast, slow} of :func:`scaled_frequencies`, or None
         self.scaling = None if not scaling else tuple(float(scaling[key]) for key in ("factor", "original", "fast", "slow"))
+        # "float32": the frequencies come from float32 arithmetic (rope.py:24-25); "float64": theta^(-2i/dims) is
+        # computed in double precision and rounded to float32 once
+        if frequencies not in ("float32", "float64"):
+            raise ValueError(f"frequencies are computed in 'float32' or 'float64', not {frequencies!r}")
+        self.frequencies = frequencies
         self.magnitude = 1.0
         self._inv_freq: Optional[torch.Tensor] = None
 
@@ -69,6 +75,9 @@ class RotaryPosition(Part):
             if self.scaling is not None:
                 frequencies, self.magnitude = scaled_frequencies(self.rotary_dim, self.theta, *self.scaling)
                 self._inv_freq = torch.tensor(frequencies, dtype=torch.float64).to(torch.float32).to(device)
+            elif self.frequencies == "float64":
+                exact = [self.theta ** (-2.0 * i / self.rotary_dim) for i in range(self.rotary_dim // 2)]
+                self._inv_freq = torch.tensor(exact, dtype=torch.float64).to(torch.float32).to(device)
             else:
                 exponents = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim
                 self._inv_freq = (1.0 / (self.theta ** exponents)).to(device)
@@ -76,7 +85,7 @@ class RotaryPosition(Part):
 
     def tables(self, ctx: StepContext) -> torch.Tensor:
         """float32 ``[N, rotary_dim/2, 2]`` of (cos, sin) times the magnitude, shared through the step's memo."""
-        key = ("rope", self.theta, self.rotary_dim, self.scaling)
+        key = ("rope", self.theta, self.rotary_dim, self.scaling, self.frequencies)
         table = ctx.memo.get(key)
         if table is None:
             table = torch.empty((ctx.n_tokens, self.rotary_dim // 2, 2), dtype=torch.float32, device=ctx.device)
