@@ -490,9 +490,27 @@ def _vesidra(width, layers, mixer, dense_ff, experts, top, expert_ff, shared_ff,
                 layers=entries)
 
 
+def _zozezen(width, heads, kv_heads, head, ssm_heads, ssm_head, state, groups, experts, identity, top, expert_ff, shared_ff, vocab):
+    """Four layers: state-space, attention, state-space, attention that reads the second layer's keys and values."""
+    attention = dict(heads=heads, kv_heads=kv_heads, dim=head, vdim=head, scale=head ** -0.5, rot=dict(base=1000000.0, dims=head // 2))
+    recurrence = dict(heads=ssm_heads, vdim=ssm_head, state=state, groups=groups, conv=4, norm_groups=groups)
+    mlp = dict(kind="moe", expert=dict(ff=expert_ff, limit=7.0),
+               router=dict(experts=experts, identity=identity, top=top, groups=dict(count=4, keep=2)), shared=dict(ff=shared_ff, limit=7.0))
+    entries = [dict(type="mamba2", mixer=recurrence, mlp=mlp), dict(type="attention", mixer=attention, mlp=mlp),
+               dict(type="mamba2", mixer=recurrence, mlp=mlp), dict(type="attention", mixer=dict(attention, kv_from=1), mlp=mlp)]
+    return dict(architecture="Zozezen", vocab=vocab, width=width, norm=dict(eps=1e-6), layers=entries)
+
+
 # Layer sizes that resemble real models' (random weights, four layers each: two with a gated MLP, two with experts), and
 # the Qwen3 layers of equal width, head count and inner size beside them.
 DESIGN_SIZES = {
+    # Zozezen: sixteen heads of 128 over four key/value heads; a recurrence of 64 heads of 64 channels with a state of 128 in
+    # eight groups; 16 experts of 1,024 (four per token, two of four groups kept) and a shared one of 2,048
+    "hybrid-small": dict(zozezen=_zozezen(2048, 16, 4, 128, 64, 64, 128, 8, 16, 0, 4, 1024, 2048, 32000),
+                         qwen3=dict(hidden_size=2048, intermediate_size=6144, num_attention_heads=16, num_key_value_heads=4, head_dim=128)),
+    # the same with heads of 64, a state of 64, and 60 experts of 1,408 beside four identity experts, six per token
+    "hybrid-lite": dict(zozezen=_zozezen(2048, 32, 8, 64, 32, 128, 64, 4, 60, 4, 6, 1408, 2816, 32000),
+                        qwen3=dict(hidden_size=2048, intermediate_size=10944, num_attention_heads=32, num_key_value_heads=8, head_dim=64)),
     # latent 256 + 32, sixteen heads of 64 + 32; 16 experts of 1,024, four per token, and a shared one of 2,048
     "small": dict(vesidra=_vesidra(2048, 4, _latent(16, 64, 32, 64, 256), 6144, 16, 4, 1024, 2048, 32000),
                   qwen3=dict(hidden_size=2048, intermediate_size=6144, num_attention_heads=16, num_key_value_heads=8, head_dim=128)),
@@ -503,7 +521,7 @@ DESIGN_SIZES = {
 
 
 def designs_workload(args) -> int:
-    """``--workload designs``: prompt and decode throughput of Vesidra at sizes that resemble real models' layers, beside
+    """``--workload designs``: prompt and decode throughput of Vesidra and of Zozezen at sizes that resemble real models' layers, beside
     the Qwen3 decoder at equal width, depth, head count and inner size; one JSON line per size and design, with each
     step's kernels (device time by kernel, from the framework profiler) so that like kernels can be set side by side."""
     import torch
@@ -520,14 +538,16 @@ def designs_workload(args) -> int:
     for size_name, pair in DESIGN_SIZES.items():
         if args.design_size and size_name != args.design_size:
             continue
-        layers = len(pair["vesidra"]["layers"])
-        vocab = pair["vesidra"]["vocab"]
-        configs = {"vesidra": pair["vesidra"],
-                   "qwen3": dict(MODEL, **pair["qwen3"], num_hidden_layers=layers, vocab_size=vocab, tie_word_embeddings=True)}
+        own = {name: config for name, config in pair.items() if name != "qwen3"}
+        layers = len(next(iter(own.values()))["layers"])
+        vocab = next(iter(own.values()))["vocab"]
+        configs = dict(own, qwen3=dict(MODEL, **pair["qwen3"], num_hidden_layers=layers, vocab_size=vocab, tie_word_embeddings=True))
         for design, config in configs.items():
-            pages = batch * ((context + steps + 8 + PAGE_SIZE - 1) // PAGE_SIZE) + prompt_tokens // PAGE_SIZE + 8
+            # (a model with per-request state cannot be cut back between the timed blocks: its contexts grow through all of them)
+            room = context + 8 * steps + warmup + 8
+            pages = batch * ((room + PAGE_SIZE - 1) // PAGE_SIZE) + prompt_tokens // PAGE_SIZE + 8
             runtime = build_runtime(None, EngineConfig(
-                dtype="bfloat16", max_model_len=max(context + steps + 8, prompt_tokens), max_num_seqs=batch + 1, kv_block_size=PAGE_SIZE,
+                dtype="bfloat16", max_model_len=max(room, prompt_tokens), max_num_seqs=batch + 1, kv_block_size=PAGE_SIZE,
                 num_kv_blocks=pages, max_num_batched_tokens=max(8192, prompt_tokens), enable_prefix_cache=False,
                 decode_execution="cuda_graph"), config_dict=config, weights_seed=0)
             manager, run = runtime.manager, runtime.step_function.run
@@ -564,7 +584,9 @@ def designs_workload(args) -> int:
             prompt = tokens_of(prompt_tokens)
 
             def prompt_step() -> None:
-                manager.admit("p")
+                slot = manager.admit("p").slot
+                if manager.state_needs:
+                    runtime.storage.reset_slot(slot, 0.0, 1.0, 0, 0)          # a new request's state starts from zero
                 reservation = manager.prepare([("p", prompt_tokens)])
                 run([StepEntry("p", prompt, [prompt_tokens - 1])], reservation)
                 manager.commit(reservation)
@@ -594,6 +616,8 @@ def designs_workload(args) -> int:
                     manager.commit(reservation)
 
             def rewind() -> None:
+                if manager.state_needs:
+                    return
                 for rid in ids:
                     manager.truncate(rid, context)
 
@@ -648,7 +672,7 @@ def main() -> int:
                         help="fewer layers than the model has (named in the output); for quick checks only")
     parser.add_argument("--skip-points", action="store_true")
     parser.add_argument("--workload", choices=("default", "mixed", "sweep", "designs"), default="default",
-                        help="designs: Vesidra beside Qwen3 at equal layer sizes (prompt and decode throughput, kernels by time)")
+                        help="designs: Vesidra and Zozezen beside Qwen3 at equal layer sizes (prompt and decode throughput, kernels by time)")
     parser.add_argument("--design-size", choices=sorted(DESIGN_SIZES), default=None, help="with --workload designs: one size only")
     parser.add_argument("--sweep-prompt", type=int, default=1024)
     parser.add_argument("--sweep-new", type=int, default=128)

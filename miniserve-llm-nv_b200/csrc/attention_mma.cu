@@ -28,7 +28,8 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
                      const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ block_tables, int table_stride,
                      const int* __restrict__ query_start, const int* __restrict__ context_lens, int page_size, int n_q,
                      int n_kv, float scale_log2, int window, __nv_bfloat16* __restrict__ out,
-                     float* __restrict__ part_o, float* __restrict__ part_lse, int num_splits) {
+                     float* __restrict__ part_o, float* __restrict__ part_lse, int num_splits, int sink,
+                     const __nv_bfloat16* __restrict__ gate, int gate_ld) {
   // The kernel before this one on the stream wrote the queries and the keys and values of this step's
   // tokens.  What the batch looks like (set up before the step's first kernel) and the keys and values of
   // earlier steps do not depend on it, so the first tiles of old keys are requested before the wait below.
@@ -85,7 +86,13 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
           const int row = thread_row(mt, half);
           if (row < rows_total) {
             const size_t index = ((size_t)(q0 + row / group) * n_q + kv_head * group + row % group);
-            part_lse[index * num_splits + split] = -INFINITY;
+            if (sink && split == 0) {           // the sink belongs to the first split: alone there it is a result of zeros with weight 1
+              float* dst = part_o + index * num_splits * D;
+              for (int c = 0; c < D; ++c) dst[c] = 0.f;
+              part_lse[index * num_splits] = 0.f;
+            } else {
+              part_lse[index * num_splits + split] = -INFINITY;
+            }
           }
         }
     }
@@ -309,8 +316,11 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
       const int row = thread_row(mt, half);
       if (row >= rows_total) continue;
       const float m = m_run[mt][half];
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      // the sink, a key of score 0 without a value: one more term of the denominator (counted once, by the first split)
+      if (sink && split == 0) l += m == -INFINITY ? 1.f : exp2f(-m * scale_log2);
+      float inv = l > 0.f ? 1.f / l : 0.f;
       const size_t index = (size_t)(q0 + row / group) * n_q + kv_head * group + row % group;
+      if (num_splits == 1 && gate != nullptr) inv /= 1.f + __expf(-__bfloat162float(gate[(size_t)(q0 + row / group) * gate_ld + kv_head * group + row % group]));
       if (num_splits == 1) {
         __nv_bfloat16* dst = out + index * D;
 #pragma unroll
@@ -324,7 +334,8 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
         for (int n = 0; n < D / 8; ++n)
           *reinterpret_cast<float2*>(dst + n * 8 + quad_col * 2) =
               make_float2(acc_o[mt][n][2 * half] * inv, acc_o[mt][n][2 * half + 1] * inv);
-        if (quad_col == 0) part_lse[index * num_splits + split] = l > 0.f ? m * scale_log2 + log2f(l) : -INFINITY;
+        if (quad_col == 0)
+          part_lse[index * num_splits + split] = l > 0.f ? (m == -INFINITY ? 0.f : m * scale_log2) + log2f(l) : -INFINITY;
       }
     }
   }
@@ -355,7 +366,8 @@ template <int D, int W, int BN, int MT, int STAGES>
 int launch_attention_mma(const void* q, const void* k_pool, const void* v_pool, const int* block_tables,
                          int table_stride, const int* query_start, const int* context_lens, int page_size, int n_q,
                          int n_kv, float scale, int window, void* out, float* part_o, float* part_lse, int num_splits,
-                         int n_requests, int max_query_len, int n_tokens, cudaStream_t stream) {
+                         int n_requests, int max_query_len, int n_tokens, int sink, const void* gate, int gate_ld,
+                         int first_token, cudaStream_t stream) {
   constexpr int BM = 16 * MT * W;
   const size_t smem = (size_t)(BM + 2 * STAGES * BN) * D * sizeof(__nv_bfloat16) + STAGES * BN * sizeof(long long);
   auto kernel = attention_mma_kernel<D, W, BN, MT, STAGES>;
@@ -374,11 +386,16 @@ int launch_attention_mma(const void* q, const void* k_pool, const void* v_pool, 
   ms::launch(kernel, grid, W * 32, smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
                                          (const __nv_bfloat16*)v_pool, block_tables, table_stride, query_start,
                                          context_lens, page_size, n_q, n_kv, scale_log2, window, (__nv_bfloat16*)out,
-                                         part_o, part_lse, num_splits);
+                                         part_o, part_lse, num_splits, sink, (const __nv_bfloat16*)gate, gate_ld);
   MS_CHECK_LAUNCH("attention_mma");
   if (num_splits > 1) {
-    const int items = n_tokens * n_q;
-    launch_attention_combine<D>(part_o, part_lse, (__nv_bfloat16*)out, num_splits, items, stream);
+    // only the rows of this launch's requests (first_token .. n_tokens) hold partial results: the rows before them belong to
+    // requests that another launch serves, and the scratch there holds whatever it held
+    const size_t skip = (size_t)first_token * n_q;
+    const int items = (n_tokens - first_token) * n_q;
+    const __nv_bfloat16* gates = gate ? (const __nv_bfloat16*)gate + (size_t)first_token * gate_ld : nullptr;
+    launch_attention_combine<D>(part_o + skip * num_splits * D, part_lse + skip * num_splits, (__nv_bfloat16*)out + skip * D,
+                                num_splits, items, stream, gates, gate_ld, n_q);
     MS_CHECK_LAUNCH("attention_combine");
   }
   return 0;
@@ -431,14 +448,18 @@ MS_EXPORT int ms_attention_mma_splits(int d, int n_requests, int n_kv, int n_q, 
 // q, out [n_tokens, n_q, d] bfloat16; pools of one layer [pages, n_kv, page_size, d]; block_tables
 // [n_requests, table_stride]; query_start [n_requests + 1]; context_lens [n_requests] (lengths after
 // this step's tokens).  Request r's tokens query_start[r] .. query_start[r+1] are the last ones of its
-// context.  num_splits > 1 needs part_o [n_tokens * n_q * num_splits * d] and part_lse
+// context.  sink != 0: the softmax's denominator gets one more term exp(0); gate (bfloat16 logits, gate[token * gate_ld +
+// head], or null): the head's output is multiplied by the sigmoid of its logit.  first_token: the first row that belongs to
+// these requests (rows before it are another launch's and are left alone).  num_splits > 1 needs part_o [n_tokens * n_q * num_splits * d] and part_lse
 // [n_tokens * n_q * num_splits] float32 scratch and is meant for steps of single tokens.
 MS_EXPORT int ms_paged_attention_mma(const void* q, const void* k_pool, const void* v_pool, const int* block_tables,
                                      int table_stride, const int* query_start, const int* context_lens,
                                      int page_size, int n_q, int n_kv, int d, float scale, int window, void* out,
                                      float* part_o, float* part_lse, int num_splits, int n_requests,
-                                     int max_query_len, int n_tokens, cudaStream_t stream) {
+                                     int max_query_len, int n_tokens, int sink, const void* gate, int gate_ld,
+                                     int first_token, cudaStream_t stream) {
   if (n_tokens == 0 || n_requests == 0) return 0;
+  MS_REQUIRE(first_token >= 0 && first_token < n_tokens, "attention: first row %d of %d", first_token, n_tokens);
   MS_REQUIRE(n_kv > 0 && n_q % n_kv == 0, "attention: %d query heads are not a multiple of %d key/value heads", n_q, n_kv);
   MS_REQUIRE(page_size > 0 && max_query_len > 0, "attention: page size %d, longest portion %d", page_size, max_query_len);
   MS_REQUIRE(num_splits >= 1 && num_splits <= 64 && (num_splits == 1 || (part_o && part_lse)),
@@ -449,7 +470,7 @@ MS_EXPORT int ms_paged_attention_mma(const void* q, const void* k_pool, const vo
 #define MS_ATTENTION_CASE(D, W, BN, MT, STAGES)                                                                       \
   return launch_attention_mma<D, W, BN, MT, STAGES>(q, k_pool, v_pool, block_tables, table_stride, query_start,       \
                                                     context_lens, page_size, n_q, n_kv, scale, window, out, part_o,  \
-                                                    part_lse, num_splits, n_requests, max_query_len, n_tokens, stream)
+                                                    part_lse, num_splits, n_requests, max_query_len, n_tokens, sink, gate, gate_ld, first_token, stream)
   if (d == 128) { if (small) { MS_ATTENTION_CASE(128, 1, 32, 1, 2); } else { MS_ATTENTION_CASE(128, 4, 64, 2, 2); } }
   if (d == 64) { if (small) { MS_ATTENTION_CASE(64, 1, 64, 1, 2); } else { MS_ATTENTION_CASE(64, 4, 64, 2, 2); } }
   if (d == 32) { if (small) { MS_ATTENTION_CASE(32, 1, 64, 1, 2); } else { MS_ATTENTION_CASE(32, 4, 64, 2, 2); } }
@@ -506,5 +527,5 @@ MS_EXPORT int ms_paged_attention_decode_static(const void* q, const void* k_pool
   // infinity when it had no keys), and a partial result is read only where that value is finite.
   return ms_paged_attention_mma(q, k_pool, v_pool, block_tables, table_stride, query_start, context_lens, page_size,
                                 n_q, n_kv, d, scale, window, out, part_o, part_lse, num_splits, n_requests, 1, n_tokens,
-                                stream);
+                                0, nullptr, 0, 0, stream);
 }

@@ -61,7 +61,8 @@ attention_turns_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_out,
                        const int* __restrict__ block_tables, int table_stride,
                        const int* __restrict__ query_start, const int* __restrict__ context_lens, int page_size, int n_q,
-                       int n_kv, float scale_log2, int window, __nv_bfloat16* __restrict__ out, int* __restrict__ error_flag) {
+                       int n_kv, float scale_log2, int window, __nv_bfloat16* __restrict__ out, int* __restrict__ error_flag,
+                       int sink, const __nv_bfloat16* __restrict__ gate, int gate_ld) {
   using L = Layout<D>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -360,7 +361,10 @@ attention_turns_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (all_ok(ok)) {
         tmem_fence_after();
         l = sums[0][local_row] + sums[1][local_row];                  // the same sum in either thread of the row
-        const float inv = l > 0.f ? 1.f / l : 0.f;
+        if (sink) l += exp2f(-m_final * scale_log2);                  // one more key of score 0 that has no value
+        float inv = l > 0.f ? 1.f / l : 0.f;
+        if (gate != nullptr && row < rows_total)                      // the head's output times sigmoid(its gate logit)
+          inv /= 1.f + __expf(-__bfloat162float(gate[(size_t)(q0 + row / group) * gate_ld + kv_head * group + row % group]));
         // Each of the row's two threads takes half of its columns.  A whole tile goes through the shared memory of
         // the queries (no longer needed; the same layout) and leaves by TMA in whole lines: a thread storing its
         // own row touches 32 lines per instruction, 1,700 cycles for the tile.  A tile that the request's rows do not
@@ -423,7 +427,8 @@ static bool encode(CUtensorMap* map, int rank, const void* base, const cuuint64_
 template <int D>
 int launch(const void* q, const void* k_pool, const void* v_pool, int n_pages, const int* block_tables, int table_stride,
            const int* query_start, const int* context_lens, int page_size, int n_q, int n_kv, float scale, int window,
-           void* out, int n_requests, int max_query_len, int n_tokens, int* error_flag, cudaStream_t stream) {
+           void* out, int n_requests, int max_query_len, int n_tokens, int* error_flag, int sink, const void* gate, int gate_ld,
+           cudaStream_t stream) {
   const int group = n_q / n_kv;
   CUtensorMap map_q, map_k, map_v, map_out;
   {
@@ -453,7 +458,7 @@ int launch(const void* q, const void* k_pool, const void* v_pool, int n_pages, c
   dim3 grid(n_kv, (unsigned)tiles, n_requests);
   cudaError_t e = ms::launch(kernel, grid, dim3(THREADS), smem, stream, map_q, map_k, map_v, map_out, block_tables, table_stride,
                              query_start, context_lens, page_size, n_q, n_kv, scale * 1.4426950408889634f, window,
-                             (__nv_bfloat16*)out, error_flag);
+                             (__nv_bfloat16*)out, error_flag, sink, (const __nv_bfloat16*)gate, gate_ld);
   if (e != cudaSuccess) MS_FAIL("attention_turns: launch failed: %s", cudaGetErrorString(e));
   return 0;
 }
@@ -463,12 +468,14 @@ int launch(const void* q, const void* k_pool, const void* v_pool, int n_pages, c
 
 using namespace ms;
 
-// Arguments and sizes as for ms_paged_attention_tcgen05 (ms_attention_tcgen05_supports answers for both).
+// Arguments and sizes as for ms_paged_attention_tcgen05 (ms_attention_tcgen05_supports answers for both), and two options:
+// sink != 0 adds exp(0) to every row's softmax denominator (a key of score 0 without a value); gate (bfloat16 logits,
+// gate[token * gate_ld + head], or null) multiplies each head's output by the sigmoid of its logit as it is stored.
 MS_EXPORT int ms_paged_attention_turns(const void* q, const void* k_pool, const void* v_pool, int n_pages,
                                        const int* block_tables, int table_stride, const int* query_start,
                                        const int* context_lens, int page_size, int n_q, int n_kv, int d, float scale,
                                        int window, void* out, int n_requests, int max_query_len, int n_tokens,
-                                       int* error_flag, cudaStream_t stream) {
+                                       int* error_flag, int sink, const void* gate, int gate_ld, cudaStream_t stream) {
   if (n_tokens == 0 || n_requests == 0) return 0;
   const int group = n_kv > 0 && n_q % n_kv == 0 ? n_q / n_kv : 0;
   MS_REQUIRE((d == 64 || d == 128) && group > 0 && group <= 128 && 128 % group == 0 && page_size >= 8 && page_size <= 128 &&
@@ -477,7 +484,7 @@ MS_EXPORT int ms_paged_attention_turns(const void* q, const void* k_pool, const 
   MS_REQUIRE(error_flag != nullptr, "attention_turns: an error flag on the device is required");
   if (d == 128)
     return t5c::launch<128>(q, k_pool, v_pool, n_pages, block_tables, table_stride, query_start, context_lens, page_size,
-                            n_q, n_kv, scale, window, out, n_requests, max_query_len, n_tokens, error_flag, stream);
+                            n_q, n_kv, scale, window, out, n_requests, max_query_len, n_tokens, error_flag, sink, gate, gate_ld, stream);
   return t5c::launch<64>(q, k_pool, v_pool, n_pages, block_tables, table_stride, query_start, context_lens, page_size, n_q,
-                         n_kv, scale, window, out, n_requests, max_query_len, n_tokens, error_flag, stream);
+                         n_kv, scale, window, out, n_requests, max_query_len, n_tokens, error_flag, sink, gate, gate_ld, stream);
 }

@@ -56,7 +56,8 @@ template <int D> __device__ __forceinline__ __nv_bfloat16* tile_ptr(__nv_bfloat1
 template <int D>
 __global__ void __launch_bounds__(128)
 attention_combine_all_at_once_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
-                         __nv_bfloat16* __restrict__ out, int num_splits, int n_items) {
+                         __nv_bfloat16* __restrict__ out, int num_splits, int n_items,
+                         const __nv_bfloat16* __restrict__ gate, int gate_ld, int n_q) {
   grid_dependency_wait();
   grid_dependency_launch();
   __shared__ float warp_acc[4][D];
@@ -89,7 +90,9 @@ attention_combine_all_at_once_kernel(const float* __restrict__ part_o, const flo
   for (int i = 0; i < D / 32; ++i) warp_acc[warp][lane + 32 * i] = acc[i];
   __syncthreads();
   if (warp == 0) {
-    const float inv = total > 0.f ? 1.f / total : 0.f;
+    float inv = total > 0.f ? 1.f / total : 0.f;
+    // (item = token * n_q + head) the head's output times sigmoid(its gate logit), where the caller has gates
+    if (gate != nullptr) inv /= 1.f + __expf(-__bfloat162float(gate[(size_t)(item / n_q) * gate_ld + item % n_q]));
 #pragma unroll
     for (int i = 0; i < D / 32; ++i) {
       const int c = lane + 32 * i;
@@ -102,7 +105,8 @@ attention_combine_all_at_once_kernel(const float* __restrict__ part_o, const flo
 template <int D>
 __global__ void __launch_bounds__(128)
 attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
-                         __nv_bfloat16* __restrict__ out, int num_splits, int n_items) {
+                         __nv_bfloat16* __restrict__ out, int num_splits, int n_items,
+                         const __nv_bfloat16* __restrict__ gate, int gate_ld, int n_q) {
   grid_dependency_wait();
   grid_dependency_launch();
   __shared__ float warp_acc[4][D];
@@ -151,7 +155,9 @@ attention_combine_kernel(const float* __restrict__ part_o, const float* __restri
   for (int i = 0; i < D / 32; ++i) warp_acc[warp][lane + 32 * i] = acc[i];
   __syncthreads();
   if (warp == 0) {
-    const float inv = total > 0.f ? 1.f / total : 0.f;
+    float inv = total > 0.f ? 1.f / total : 0.f;
+    // (item = token * n_q + head) the head's output times sigmoid(its gate logit), where the caller has gates
+    if (gate != nullptr) inv /= 1.f + __expf(-__bfloat162float(gate[(size_t)(item / n_q) * gate_ld + item % n_q]));
 #pragma unroll
     for (int i = 0; i < D / 32; ++i) {
       const int c = lane + 32 * i;
@@ -164,11 +170,13 @@ attention_combine_kernel(const float* __restrict__ part_o, const float* __restri
 // Sixteen splits or fewer: the kernel that fetches sixteen at a time and has no code for the rest on its path.
 template <int D>
 inline void launch_attention_combine(const float* part_o, const float* part_lse, __nv_bfloat16* out, int num_splits,
-                                     int items, cudaStream_t stream) {
+                                     int items, cudaStream_t stream, const __nv_bfloat16* gate = nullptr, int gate_ld = 0,
+                                     int n_q = 1) {
   if (num_splits > 16)
-    ms::launch(attention_combine_all_at_once_kernel<D>, items, 128, 0, stream, part_o, part_lse, out, num_splits, items);
+    ms::launch(attention_combine_all_at_once_kernel<D>, items, 128, 0, stream, part_o, part_lse, out, num_splits, items, gate,
+               gate_ld, n_q);
   else
-    ms::launch(attention_combine_kernel<D>, items, 128, 0, stream, part_o, part_lse, out, num_splits, items);
+    ms::launch(attention_combine_kernel<D>, items, 128, 0, stream, part_o, part_lse, out, num_splits, items, gate, gate_ld, n_q);
 }
 
 }  // namespace ms

@@ -347,7 +347,7 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     modified = bool(softcap) or bias_slopes is not None
     if bias_slopes is not None:
         _want(bias_slopes, "bias_slopes", torch.float32, (n_q,))
-    general = modified or sink or gate is not None or value_dim != head_dim
+    general = modified or value_dim != head_dim      # (the tensor-core kernels take the sink and the gate, not these)
     if general or q.dtype != torch.bfloat16 or not lib.ms_attention_mma_supports(_i(head_dim)):
         _check(lib.ms_paged_attention_generic(
             _ptr(q), _i(_code(q.dtype)), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _i(block_tables.shape[1]),
@@ -356,19 +356,26 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
             _i(n), _i(value_dim), _i(1 if sink else 0), gate_ptr, _i(gate_ld), _stream()))
         return
 
-    def run(first: int, last: int, longest: int, rows: int) -> None:
+    def run(first: int, last: int, longest: int, rows: int, first_row: int = 0) -> None:
         """Requests first .. last - 1 (their tokens are found through query_start, which holds absolute rows);
         ``rows``: one past the last row of the batch that these requests own, which sizes the scratch of the
-        key splits and the merge that follows them."""
+        key splits and the merge that follows them; ``first_row``: their first row (the merge leaves the rows
+        before it alone: they belong to the requests of another launch)."""
         tables, starts, lens = block_tables[first:last], query_start[first:last + 1], context_lens[first:last]
         count = last - first
         group = n_q // n_kv
-        if (USE_TCGEN05_ATTENTION and longest * group > 16
+        if (USE_TCGEN05_ATTENTION and longest * group > 16 and (ATTENTION_IN_TURNS or not (sink or gate is not None))
                 and lib.ms_attention_tcgen05_supports(_i(head_dim), _i(n_q), _i(n_kv), _i(k_pool.shape[2]))):
             # prompt portions: the TMA + tcgen05 + tensor-memory kernel, its softmax groups taking the key tiles in
-            # turn or working on each together
-            entry = lib.ms_paged_attention_turns if ATTENTION_IN_TURNS else lib.ms_paged_attention_tcgen05
-            _check(entry(
+            # turn (that form also takes the sink and the gate) or working on each together
+            if ATTENTION_IN_TURNS:
+                _check(lib.ms_paged_attention_turns(
+                    _ptr(q), _ptr(k_pool), _ptr(v_pool), _i(k_pool.shape[0]), _ptr(tables), _i(block_tables.shape[1]),
+                    _ptr(starts), _ptr(lens), _i(k_pool.shape[2]), _i(n_q), _i(n_kv), _i(head_dim), _f(scale),
+                    _i(window if window else 0), _ptr(out), _i(count), _i(longest), _i(n),
+                    _ptr(device_error_flag(q.device)), _i(1 if sink else 0), gate_ptr, _i(gate_ld), _stream()))
+                return
+            _check(lib.ms_paged_attention_tcgen05(
                 _ptr(q), _ptr(k_pool), _ptr(v_pool), _i(k_pool.shape[0]), _ptr(tables), _i(block_tables.shape[1]),
                 _ptr(starts), _ptr(lens), _i(k_pool.shape[2]), _i(n_q), _i(n_kv), _i(head_dim), _f(scale),
                 _i(window if window else 0), _ptr(out), _i(count), _i(longest), _i(n),
@@ -382,7 +389,8 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         _check(lib.ms_paged_attention_mma(
             _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(tables), _i(block_tables.shape[1]), _ptr(starts), _ptr(lens),
             _i(k_pool.shape[2]), _i(n_q), _i(n_kv), _i(head_dim), _f(scale), _i(window if window else 0), _ptr(out),
-            _ptr(part_o), _ptr(part_lse), _i(splits), _i(count), _i(longest), _i(rows), _stream()))
+            _ptr(part_o), _ptr(part_lse), _i(splits), _i(count), _i(longest), _i(rows), _i(1 if sink else 0), gate_ptr,
+            _i(gate_ld), _i(first_row), _stream()))
 
     leading_single = 0
     if host_query_start and max_query_len > 1 and len(host_query_start) == n_requests + 1:
@@ -391,7 +399,7 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
             leading_single += 1
     if 0 < leading_single < n_requests:
         run(0, leading_single, 1, leading_single)      # single tokens are the batch's first rows, one each
-        run(leading_single, n_requests, max_query_len, n)
+        run(leading_single, n_requests, max_query_len, n, leading_single)
     else:
         run(0, n_requests, max_query_len, n)
 

@@ -152,7 +152,7 @@ def test_cuttings_match_plain_on_cpu(cpu_runtime, name, page_size, cutting):
     for index, entry in enumerate(config["layers"]):
         if entry["mlp"]:
             h = plain.norm_one_plus(weights["embed"], weights[f"l{index}.norm2"], config["norm"]["eps"])
-            assert plain.route(h, weights, f"l{index}.", entry["mlp"])[2] > 0.003       # (roughly: the marks decide)
+            assert plain.route(h, weights, f"l{index}.", entry["mlp"])[2] > 0.0015      # (the marks decide, then the correction's steps)
     for rid, tokens in requests.items():
         expected = plain.forward(tokens, weights, config)
         assert sorted(got[rid]) == list(range(len(tokens)))

@@ -201,6 +201,56 @@ def test_router_with_negative_choice_scores_and_ties():
     assert torch.allclose(weights.cpu(), torch.gather(scores, 1, ids.cpu().long()), atol=1e-6)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_q,n_kv,d,dv,page", [(8, 1, 64, 64, 16), (4, 2, 128, 128, 8), (6, 3, 32, 32, 16), (6, 3, 24, 40, 4), (16, 4, 128, 128, 64)])
+@pytest.mark.parametrize("single", [False, True])
+def test_attention_kernels_with_sink_and_gate(dtype, n_q, n_kv, d, dv, page, single):
+    """``paged_attention`` with the sink and the gate over unequal requests: prompt portions that continue long contexts, or
+    (``single``) one token per request over contexts of up to a few thousand keys, whose keys the tensor-core kernel cuts
+    into ranges (the sink must be counted once, also where a range is empty).  Scores lie well below zero, so that the
+    sink holds much of the weight; one key far back in every request stands out."""
+    from miniserve_b200 import kernels
+
+    contexts = [1, 70, 1500, 3000] if single else [40, 300, 129, 1000]
+    new = [1, 1, 1, 1] if single else [40, 130, 2, 257]
+    n_pages = sum((c + page - 1) // page for c in contexts)
+    k_pool, v_pool = rand((n_pages + 1, n_kv, page, d), dtype, 40, 1.0), rand((n_pages + 1, n_kv, page, dv), dtype, 41, 1.0)
+    width = max((c + page - 1) // page for c in contexts)
+    tables = torch.full((len(contexts), width), n_pages, dtype=torch.int32)
+    order = torch.randperm(n_pages, generator=torch.Generator().manual_seed(3)).int()
+    at = 0
+    for r, c in enumerate(contexts):
+        count = (c + page - 1) // page
+        tables[r, :count] = order[at:at + count]
+        at += count
+    starts = [0]
+    for count in new:
+        starts.append(starts[-1] + count)
+    n = starts[-1]
+    q = rand((n, n_q, d), dtype, 42, 1.0)
+    q[..., 0] = 10.0
+    k_pool[..., 0] = -10.0                      # every score gets -100 * scale: far below the sink's 0
+    for r, c in enumerate(contexts):            # but one key far back in each request points the queries' way
+        far = max(0, c - new[r] - 900) if c > 10 else 0
+        k_pool[tables[r, far // page].long(), :, far % page, 0] = 0.5      # (its weight is of the sink's order)
+    request_of = torch.cat([torch.full((count,), r, dtype=torch.int32) for r, count in enumerate(new)]).cuda()
+    positions = torch.cat([torch.arange(c - count, c, dtype=torch.int32) for c, count in zip(contexts, new)]).cuda()
+    gate = rand((n, n_q + 5), dtype, 43, 2.0)
+    scale = 0.11
+    out = torch.empty((n, n_q, dv), dtype=dtype).cuda()
+    args = [torch.tensor(starts, dtype=torch.int32).cuda(), torch.tensor(contexts, dtype=torch.int32).cuda(), max(new), max(contexts), scale, None]
+    kernels.paged_attention(q, k_pool, v_pool, tables.cuda(), request_of, positions, *args, out, starts, sink=True, gate=gate, gate_col=3)
+    expected = cpu(out)
+    plain_ops.paged_attention(cpu(q), cpu(k_pool), cpu(v_pool), tables, cpu(request_of), cpu(positions), *[cpu(a) if torch.is_tensor(a) else a for a in args],
+                              expected, sink=True, gate=cpu(gate), gate_col=3)
+    kernels.check_device_errors(q.device)
+    assert torch.allclose(out.cpu().double(), expected.double(), **tol(dtype, float(expected.abs().max())))
+    no_sink = cpu(out)
+    plain_ops.paged_attention(cpu(q), cpu(k_pool), cpu(v_pool), tables, cpu(request_of), cpu(positions), *[cpu(a) if torch.is_tensor(a) else a for a in args],
+                              no_sink, sink=False, gate=cpu(gate), gate_col=3)
+    assert float((no_sink.double() - expected.double()).abs().max()) > 0.1 * float(expected.abs().max())     # the sink decides
+
+
 # --------------------------------------------------------------------------- parts alone
 
 

@@ -68,8 +68,10 @@ def steer_routers(tensors: dict, config: dict) -> None:
     """Makes every router's choice clear.  Every routed layer gets columns of its own in the embedding: a token's row carries
     the marks 16, 12, 9, ... in the columns of the router outputs id, id + 1, ... (mod the number of outputs), as many as the
     layer chooses, and nothing in the layer's other columns.  The router reads only its own columns (weight one quarter), the
-    correction of the choice is ``0.006 * index - 0.5`` (all choice scores negative, no two outputs level), and the norms of
-    the sublayers' outputs have small weights, so that the stream keeps the marks through all layers.  In place."""
+    correction of the choice is ``-0.3 - index / 512`` (all choice scores negative, no two outputs level, and the steps survive
+    a bfloat16 checkpoint), and the norms of the sublayers' outputs have small weights, and exactly none in the columns of the
+    marks: the stream keeps the marks through all layers untouched, so outputs without a mark score exactly alike and the
+    correction alone ranks them.  In place."""
     vocab, width = config["vocab"], config["width"]
     ids = torch.arange(vocab)
     embed = tensors["embed"].float()
@@ -95,10 +97,13 @@ def steer_routers(tensors: dict, config: dict) -> None:
         weight = torch.zeros(total, width)
         weight[:, column:column + total] = 0.25 * torch.eye(total)
         tensors[name] = weight.to(tensors[name].dtype)
-        tensors[f"l{index}.mlp.correction"] = (0.006 * torch.arange(total, dtype=torch.float32) - 0.5).to(tensors[f"l{index}.mlp.correction"].dtype)
+        tensors[f"l{index}.mlp.correction"] = (-0.3 - torch.arange(total, dtype=torch.float32) / 512).to(tensors[f"l{index}.mlp.correction"].dtype)
         column += total
     if column > width:
         raise ValueError("the width is too small for the marks of all routed layers")
+    for name in tensors:
+        if name.endswith((".norm1b", ".norm2b")):
+            tensors[name][:column] = -1.0
     tensors["embed"] = embed.to(tensors["embed"].dtype)
 
 
