@@ -86,84 +86,184 @@ causal_conv_silu_kernel(const T* __restrict__ proj, int ld, int col, int channel
   }
 }
 
-// The recurrence.  grid (column blocks of a head, heads, requests); a block of 128 threads owns 16 channels (columns p) of
-// one head of one request: 8 lanes per column, lane j holding the state entries n = j, j + 8, ... (R of them) in
-// registers.  Tokens are staged through shared memory in chunks; y_t[p] is the lanes' partial sums added by a fixed tree.
-constexpr int kScanLanes = 8, kScanColumns = 16, kScanChunk = 16;
+// The recurrence.  grid (column blocks of a head, heads, requests); a block of four warps owns 4 * CP channels (columns p)
+// of one head of one request, a warp CP of them, with the 32 lanes along the state: lane j holds the entries n = j,
+// j + 32, ... (R of them) of each of its columns in registers.  The tokens' B, C and x pass through shared memory in chunks
+// of TOK tokens, two chunks deep: the asynchronous copies of the next chunk run while this one is multiplied, so the trip to
+// the second-level cache is paid once per kernel, not once per token.  Step sizes and decays (a softplus and two
+// exponentials per token and head) are computed for a chunk at a time, lane l taking token l, and handed round by shuffles.
+// y_t[p] for the warp's CP columns is reduced across the lanes in one butterfly that halves the number of values a lane
+// carries at each of its first steps (six shuffles for four columns, not twenty); the order of every sum is fixed.
+constexpr int kScanWarps = 4;
 
-template <typename T, int R>
-__global__ void __launch_bounds__(kScanLanes * kScanColumns)
+__device__ __forceinline__ void scan_copy(float* dst, const float* src, bool valid, bool wide) {
+  const unsigned to = (unsigned)__cvta_generic_to_shared(dst);
+  if (wide) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(to), "l"(src), "r"(valid ? 16 : 0));
+  } else {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(to), "l"(src), "r"(valid ? 4 : 0));
+  }
+}
+
+// FULL: the state is a multiple of 32 numbers and the head's channels a multiple of the block's (no lane or column is idle,
+// and no bound is tested per token).
+template <typename T, int R, int CP, int TOK, bool FULL>
+__global__ void __launch_bounds__(kScanWarps * 32)
 selective_scan_kernel(const float* __restrict__ conv, int conv_ld, const T* __restrict__ proj, int ld, int dt_col,
                       const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                       float* __restrict__ states, long long state_stride, int state_offset,
                       const int* __restrict__ state_slots, const int* __restrict__ query_start, int heads, int P, int N,
-                      int groups, float* __restrict__ y) {
+                      int groups, float* __restrict__ y, int wide) {
   grid_dependency_wait();
   grid_dependency_launch();
-  extern __shared__ float scan_smem[];
-  float* b_s = scan_smem;                         // [chunk][N]
-  float* c_s = b_s + kScanChunk * N;              // [chunk][N]
-  float* x_s = c_s + kScanChunk * N;              // [chunk][columns]
-  float* dt_s = x_s + kScanChunk * kScanColumns;  // [chunk]: step size
-  float* decay_s = dt_s + kScanChunk;             // [chunk]
+  constexpr int COLS = kScanWarps * CP;
+  extern __shared__ __align__(16) float scan_smem[];
+  const int n_pad = (N + 3) & ~3;                           // a token's B (or C) row in shared memory
+  const int stage_floats = TOK * (2 * n_pad + COLS);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int head = blockIdx.y, request = blockIdx.z;
-  const int p0 = blockIdx.x * kScanColumns;
-  const int tid = threadIdx.x, lane = tid % kScanLanes, column = tid / kScanLanes;
-  const int p = p0 + column;
+  const int block_p0 = blockIdx.x * COLS, p0 = block_p0 + warp * CP;
   const int q0 = query_start[request], q_len = query_start[request + 1] - q0;
-  if (q_len <= 0) return;
+  if (q_len <= 0) return;                                   // (the whole block)
   const int group = head / (heads / groups);
   const int inner = heads * P;
-  float* state = states + (long long)state_slots[request] * state_stride + state_offset + ((size_t)head * P + p) * N;
-  float s[R];
+  const float* conv_x = conv + (size_t)q0 * conv_ld + head * P + block_p0;
+  const float* conv_b = conv + (size_t)q0 * conv_ld + inner + group * N;
+  const float* conv_c = conv_b + (size_t)groups * N;
+  float* y_row = y + (size_t)q0 * inner + head * P + p0;
+  float* state = states + (long long)state_slots[request] * state_stride + state_offset + ((size_t)head * P + p0) * N;
+
+  // one chunk's copies: rows of B and C (n_pad floats each, in pieces of four floats or single floats) and COLS values of x
+  auto fetch = [&](int chunk, int stage) {
+    float* b_s = scan_smem + stage * stage_floats;
+    float* c_s = b_s + TOK * n_pad;
+    float* x_s = c_s + TOK * n_pad;
+    const int t0 = chunk * TOK;
+    if (wide) {
+      const int pieces = n_pad / 4;
+      for (int i = tid; i < TOK * pieces; i += kScanWarps * 32) {
+        const int t = i / pieces, piece = (i % pieces) * 4;
+        const bool valid = t0 + t < q_len;
+        const size_t row = valid ? (size_t)(t0 + t) * conv_ld : 0;
+        scan_copy(b_s + t * n_pad + piece, conv_b + row + piece, valid, true);
+        scan_copy(c_s + t * n_pad + piece, conv_c + row + piece, valid, true);
+      }
+    } else {
+      for (int i = tid; i < TOK * N; i += kScanWarps * 32) {
+        const int t = i / N, n = i % N;
+        const bool valid = t0 + t < q_len;
+        const size_t row = valid ? (size_t)(t0 + t) * conv_ld : 0;
+        scan_copy(b_s + t * n_pad + n, conv_b + row + n, valid, false);
+        scan_copy(c_s + t * n_pad + n, conv_c + row + n, valid, false);
+      }
+    }
+    for (int i = tid; i < TOK * COLS; i += kScanWarps * 32) {
+      const int t = i / COLS, col = i % COLS;
+      const bool valid = t0 + t < q_len && block_p0 + col < P;
+      scan_copy(x_s + i, conv_x + (valid ? (size_t)(t0 + t) * conv_ld + col : 0), valid, false);
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+
+  const int chunks = (q_len + TOK - 1) / TOK;
+  fetch(0, 0);
+  float s[CP][R];
 #pragma unroll
-  for (int i = 0; i < R; ++i) {
-    const int n = lane + kScanLanes * i;
-    s[i] = (p < P && n < N) ? state[n] : 0.f;
-  }
+  for (int cp = 0; cp < CP; ++cp)
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int n = lane + 32 * r;
+      s[cp][r] = (p0 + cp < P && n < N) ? state[(size_t)cp * N + n] : 0.f;
+    }
   const float a = -expf(a_log[head]);
   const float bias = dt_bias[head], skip = d_skip[head];
-  for (int t0 = 0; t0 < q_len; t0 += kScanChunk) {
-    const int count = min(kScanChunk, q_len - t0);
-    __syncthreads();
-    for (int i = tid; i < count * N; i += blockDim.x) {
-      const int t = i / N, n = i % N;
-      const float* row = conv + (size_t)(q0 + t0 + t) * conv_ld + inner + group * N + n;
-      b_s[t * N + n] = row[0];
-      c_s[t * N + n] = row[(size_t)groups * N];
-    }
-    for (int i = tid; i < count * kScanColumns; i += blockDim.x) {
-      const int t = i / kScanColumns, cc = i % kScanColumns;
-      x_s[i] = p0 + cc < P ? conv[(size_t)(q0 + t0 + t) * conv_ld + head * P + p0 + cc] : 0.f;
-    }
-    if (tid < count) {
-      const float raw = to_float(proj[(size_t)(q0 + t0 + tid) * ld + dt_col + head]) + bias;
-      const float step = raw > 20.f ? raw : log1pf(expf(raw));        // softplus; above 20 the two agree in float32
-      dt_s[tid] = step;
-      decay_s[tid] = expf(a * step);
+  auto raw_step = [&](int chunk) {                          // the step-size logit of token chunk * TOK + lane
+    const int t = chunk * TOK + lane;
+    return (lane < TOK && t < q_len) ? to_float(proj[(size_t)(q0 + t) * ld + dt_col + head]) : 0.f;
+  };
+  float raw_next = raw_step(0);
+  for (int chunk = 0; chunk < chunks; ++chunk) {
+    const float raw = raw_next + bias;
+    if (chunk + 1 < chunks) {
+      fetch(chunk + 1, (chunk + 1) & 1);
+      raw_next = raw_step(chunk + 1);
+      asm volatile("cp.async.wait_group 1;\n" ::);
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::);
     }
     __syncthreads();
-    for (int t = 0; t < count; ++t) {
-      const float decay = decay_s[t], xv = x_s[t * kScanColumns + column], in = dt_s[t] * xv;
-      float partial = 0.f;
+    const float my_step = raw > 20.f ? raw : log1pf(expf(raw));         // softplus; above 20 the two agree in float32
+    const float my_decay = expf(a * my_step);
+    const float* b_s = scan_smem + (chunk & 1) * stage_floats;
+    const float* c_s = b_s + TOK * n_pad;
+    const float* x_s = c_s + TOK * n_pad + warp * CP;
+    const int t0 = chunk * TOK, count = min(TOK, q_len - t0);
+    if (p0 < P) {
+      float* y_at = y_row + (size_t)t0 * inner;
+#pragma unroll 4
+      for (int u = 0; u < count; ++u, y_at += inner) {
+        float b[R], c[R], x[CP];
 #pragma unroll
-      for (int i = 0; i < R; ++i) {
-        const int n = lane + kScanLanes * i;
-        if (n < N) {
-          s[i] = decay * s[i] + in * b_s[t * N + n];
-          partial += s[i] * c_s[t * N + n];
+        for (int r = 0; r < R; ++r) {
+          const int n = lane + 32 * r;
+          b[r] = (FULL || n < N) ? b_s[u * n_pad + n] : 0.f;
+          c[r] = (FULL || n < N) ? c_s[u * n_pad + n] : 0.f;
         }
-      }
-      partial += __shfl_xor_sync(0xffffffffu, partial, 1);
-      partial += __shfl_xor_sync(0xffffffffu, partial, 2);
-      partial += __shfl_xor_sync(0xffffffffu, partial, 4);
-      if (lane == 0 && p < P) y[(size_t)(q0 + t0 + t) * inner + head * P + p] = partial + skip * xv;
-    }
-  }
+        if constexpr (CP == 4) {                            // (16-byte aligned: COLS and CP are multiples of four)
+          const float4 four = *reinterpret_cast<const float4*>(x_s + u * COLS);
+          x[0] = four.x, x[1] = four.y, x[2] = four.z, x[3] = four.w;
+        } else {
 #pragma unroll
-  for (int i = 0; i < R; ++i) {
-    const int n = lane + kScanLanes * i;
-    if (p < P && n < N) state[n] = s[i];
+          for (int cp = 0; cp < CP; ++cp) x[cp] = x_s[u * COLS + cp];
+        }
+        const float step = __shfl_sync(0xffffffffu, my_step, u), decay = __shfl_sync(0xffffffffu, my_decay, u);
+        float partial[CP];
+#pragma unroll
+        for (int cp = 0; cp < CP; ++cp) {
+          const float in = step * x[cp];
+          float sum = 0.f;
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            s[cp][r] = decay * s[cp][r] + in * b[r];
+            sum += s[cp][r] * c[r];
+          }
+          partial[cp] = sum;
+        }
+        // butterfly: the upper half of the lanes goes on with the upper half of the columns, and so on; the lanes
+        // 0, 32 / CP, 2 * 32 / CP, ... end up with the totals of columns 0, 1, 2, ...
+        float value, mine_x;
+        if constexpr (CP == 4) {
+          const bool upper = lane & 16;
+          const float keep0 = upper ? partial[2] : partial[0], keep1 = upper ? partial[3] : partial[1];
+          const float give0 = upper ? partial[0] : partial[2], give1 = upper ? partial[1] : partial[3];
+          const float v0 = keep0 + __shfl_xor_sync(0xffffffffu, give0, 16), v1 = keep1 + __shfl_xor_sync(0xffffffffu, give1, 16);
+          const bool second = lane & 8;
+          value = (second ? v1 : v0) + __shfl_xor_sync(0xffffffffu, second ? v0 : v1, 8);
+          value += __shfl_xor_sync(0xffffffffu, value, 4);
+          mine_x = upper ? (second ? x[3] : x[2]) : (second ? x[1] : x[0]);
+        } else {
+          const bool upper = lane & 16;
+          value = (upper ? partial[CP - 1] : partial[0]) + __shfl_xor_sync(0xffffffffu, upper ? partial[0] : partial[CP - 1], 16);
+          value += __shfl_xor_sync(0xffffffffu, value, 8);
+          value += __shfl_xor_sync(0xffffffffu, value, 4);
+          mine_x = upper ? x[CP - 1] : x[0];
+        }
+        value += __shfl_xor_sync(0xffffffffu, value, 2);
+        value += __shfl_xor_sync(0xffffffffu, value, 1);
+        const int column = lane / (32 / CP);
+        if ((lane & (32 / CP - 1)) == 0 && (FULL || p0 + column < P)) y_at[column] = value + skip * mine_x;
+      }
+    }
+    __syncthreads();                                        // the stage may be refilled
+  }
+  if (p0 < P) {
+#pragma unroll
+    for (int cp = 0; cp < CP; ++cp)
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const int n = lane + 32 * r;
+        if (p0 + cp < P && n < N) state[(size_t)cp * N + n] = s[cp][r];
+      }
   }
 }
 
@@ -216,7 +316,9 @@ MS_EXPORT int ms_causal_conv_silu(const void* proj, int dtype, int ld, int col, 
   return 0;
 }
 
-MS_EXPORT int ms_scan_max_state() { return kScanLanes * 32; }
+constexpr int kScanMaxState = 256;      // 32 lanes with up to eight entries each
+
+MS_EXPORT int ms_scan_max_state() { return kScanMaxState; }
 
 // conv float32 [tokens, conv_ld] = [x: heads * P | B: groups * N | C: groups * N]; dt is column dt_col + head of proj;
 // dt_bias, a_log, d float32 [heads]; the heads' states [heads][P][N] at state_offset of a slot's row; y float32
@@ -227,18 +329,32 @@ MS_EXPORT int ms_selective_scan(const float* conv, int conv_ld, const void* proj
                                 int n_requests, int heads, int p, int n_state, int groups, float* y, cudaStream_t stream) {
   if (n_requests == 0) return 0;
   MS_REQUIRE(heads > 0 && groups > 0 && heads % groups == 0, "selective_scan: %d heads in %d groups", heads, groups);
-  MS_REQUIRE(n_state >= 1 && n_state <= kScanLanes * 32, "selective_scan: a state of %d numbers per channel outside 1..%d",
-             n_state, kScanLanes * 32);
+  MS_REQUIRE(n_state >= 1 && n_state <= kScanMaxState, "selective_scan: a state of %d numbers per channel outside 1..%d",
+             n_state, kScanMaxState);
   MS_REQUIRE(heads <= 65535 && n_requests <= 65535, "selective_scan: grid exceeds the launch limits");
-  dim3 grid((p + kScanColumns - 1) / kScanColumns, heads, n_requests);
-  const size_t smem = (size_t)(2 * kScanChunk * n_state + kScanChunk * kScanColumns + 2 * kScanChunk) * sizeof(float);
-  const int per_lane = (n_state + kScanLanes - 1) / kScanLanes;
-#define MS_SCAN(R)                                                                                                          \
-  MS_SS_DISPATCH(dtype, (ms::launch(selective_scan_kernel<T, R>, grid, kScanLanes * kScanColumns, smem, stream, conv, conv_ld, \
-                                    (const T*)proj, ld, dt_col, dt_bias, a_log, d, states, state_stride, state_offset,       \
-                                    state_slots, query_start, heads, p, n_state, groups, y)))
-  if (per_lane <= 2) { MS_SCAN(2); } else if (per_lane <= 4) { MS_SCAN(4); } else if (per_lane <= 8) { MS_SCAN(8); }
-  else if (per_lane <= 16) { MS_SCAN(16); } else { MS_SCAN(32); }
+  const int per_lane = (n_state + 31) / 32;
+  // the copies into shared memory move four floats at a time where every row of B and C starts on a 16-byte boundary
+  const int inner = heads * p;
+  const int wide = (n_state % 4 == 0 && conv_ld % 4 == 0 && inner % 4 == 0 && (reinterpret_cast<uintptr_t>(conv) & 15) == 0) ? 1 : 0;
+  const int full = (n_state % 32 == 0 && p % (kScanWarps * (per_lane <= 4 ? 4 : 2)) == 0) ? 1 : 0;
+  // columns per warp: four where a lane holds few entries (more products per load), two where it holds many
+#define MS_SCAN(R, CP, TOK)                                                                                                    \
+  {                                                                                                                            \
+    dim3 grid((p + kScanWarps * CP - 1) / (kScanWarps * CP), heads, n_requests);                                              \
+    const size_t smem = (size_t)2 * TOK * (2 * ((n_state + 3) & ~3) + kScanWarps * CP) * sizeof(float);                        \
+    MS_SS_DISPATCH(dtype, {                                                                                                    \
+      auto kernel = full ? selective_scan_kernel<T, R, CP, TOK, true> : selective_scan_kernel<T, R, CP, TOK, false>;           \
+      static bool configured[2] = {false, false};                                                                                          \
+      if (!configured[full]) {                                                                                                 \
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * TOK * (2 * 32 * R + kScanWarps * CP) * 4); \
+        if (e != cudaSuccess) MS_FAIL("selective_scan: shared memory refused: %s", cudaGetErrorString(e));                     \
+        configured[full] = true;                                                                                               \
+      }                                                                                                                        \
+      ms::launch(kernel, grid, kScanWarps * 32, smem, stream, conv, conv_ld, (const T*)proj, ld, dt_col, dt_bias, a_log, d,    \
+                 states, state_stride, state_offset, state_slots, query_start, heads, p, n_state, groups, y, wide);            \
+    })                                                                                                                         \
+  }
+  if (per_lane <= 1) MS_SCAN(1, 4, 32) else if (per_lane <= 2) MS_SCAN(2, 4, 32) else if (per_lane <= 4) MS_SCAN(4, 4, 32) else MS_SCAN(8, 2, 16)
 #undef MS_SCAN
   MS_CHECK_LAUNCH("selective_scan");
   return 0;
