@@ -8,6 +8,7 @@
 //
 // All arithmetic is float32; storage is float32 or bfloat16.
 #include "common.cuh"
+#include "elementwise_vec.cuh"
 
 namespace ms {
 
@@ -55,6 +56,62 @@ __global__ void postnorm_add_rmsnorm_kernel(float* __restrict__ residual, const 
   for (int i = 0; i < kPostNormPerThread; ++i) {
     const int c = threadIdx.x + i * blockDim.x;
     if (c < hidden) dst[c] = from_float<T>(load_as_float(weight, weight_dtype, c) * (v[i] * inv));
+  }
+}
+
+// The same with sixteen-byte loads and stores: each thread keeps up to CHUNKS groups of eight elements in registers, so
+// every row is read once.  Requires hidden % 8 == 0 and hidden <= 8 * blockDim.x * CHUNKS.
+template <typename T, int CHUNKS>
+__global__ void postnorm_add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                                const void* __restrict__ post_weight, int post_weight_dtype, float post_eps,
+                                                const void* __restrict__ weight, int weight_dtype, float eps,
+                                                const int* __restrict__ rows, T* __restrict__ out, int hidden) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  __shared__ float scratch[32];
+  const size_t k = blockIdx.x;
+  const size_t r = rows ? (size_t)rows[k] : k;
+  float* res = residual + r * hidden;
+  const T* del = delta + r * hidden;
+  Vec8 v[CHUNKS], x[CHUNKS];
+  float sum_sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < CHUNKS; ++i) {
+    const int c = (i * blockDim.x + threadIdx.x) * 8;
+    if (c < hidden) {
+      v[i] = load8(del + c);
+      x[i] = load8(res + c);                               // (on its way while the first sum is formed)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sum_sq += v[i].v[e] * v[i].v[e];
+    }
+  }
+  const float inv_delta = 1.0f / sqrtf(block_sum(sum_sq, scratch) / (float)hidden + post_eps);
+  sum_sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < CHUNKS; ++i) {
+    const int c = (i * blockDim.x + threadIdx.x) * 8;
+    if (c < hidden) {
+      const Vec8 w = load8_any(post_weight, post_weight_dtype, c);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        x[i].v[e] += w.v[e] * (v[i].v[e] * inv_delta);
+        sum_sq += x[i].v[e] * x[i].v[e];
+      }
+      if (rows == nullptr) store8(res + c, x[i]);
+    }
+  }
+  const float inv = 1.0f / sqrtf(block_sum(sum_sq, scratch) / (float)hidden + eps);
+  T* dst = out + k * hidden;
+#pragma unroll
+  for (int i = 0; i < CHUNKS; ++i) {
+    const int c = (i * blockDim.x + threadIdx.x) * 8;
+    if (c < hidden) {
+      const Vec8 w = load8_any(weight, weight_dtype, c);
+      Vec8 y;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y.v[e] = w.v[e] * (x[i].v[e] * inv);
+      store8(dst + c, y);
+    }
   }
 }
 
@@ -149,6 +206,19 @@ MS_EXPORT int ms_postnorm_add_rmsnorm(float* residual, const void* delta, int dt
   if (n_out == 0) return 0;
   MS_REQUIRE(hidden > 0 && hidden <= 1024 * kPostNormPerThread, "postnorm_add_rmsnorm: width %d outside 1..%d", hidden,
              1024 * kPostNormPerThread);
+  if (hidden % 8 == 0 && hidden <= 8192) {
+    const int groups = hidden / 8;
+    const int vec_threads = groups >= 256 ? 256 : ((groups + 31) / 32) * 32;
+    const int chunks = (groups + vec_threads - 1) / vec_threads;
+#define MS_POSTNORM_VEC(C)                                                                                                   \
+  MS_EG_DISPATCH(dtype, (ms::launch(postnorm_add_rmsnorm_vec_kernel<T, C>, n_out, vec_threads, 0, stream, residual,          \
+                                    (const T*)delta, post_weight, post_weight_dtype, post_eps, weight, weight_dtype, eps,   \
+                                    rows, (T*)out, hidden)))
+    if (chunks == 1) { MS_POSTNORM_VEC(1); } else if (chunks == 2) { MS_POSTNORM_VEC(2); } else { MS_POSTNORM_VEC(4); }
+#undef MS_POSTNORM_VEC
+    MS_CHECK_LAUNCH("postnorm_add_rmsnorm");
+    return 0;
+  }
   int threads = ((hidden + kPostNormPerThread - 1) / kPostNormPerThread + 31) / 32 * 32;
   if (threads < 128 && hidden >= 128) threads = 128;
   if (hidden >= 2048 && threads < 256) threads = 256;

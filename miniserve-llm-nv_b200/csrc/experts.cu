@@ -642,10 +642,41 @@ MS_EXPORT int ms_relu_square(void* x, int dtype, long long total, cudaStream_t s
   return 0;
 }
 
+namespace ms {
+// Eight results per thread: two sixteen-byte loads of (gate, up) pairs, one store (bfloat16; total % 8 == 0).
+__global__ void clamped_glu_vec_kernel(const __nv_bfloat16* __restrict__ both, __nv_bfloat16* __restrict__ out, size_t groups,
+                                       float limit) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= groups) return;
+  const uint4 lo = *reinterpret_cast<const uint4*>(both + 16 * i), hi = *reinterpret_cast<const uint4*>(both + 16 * i + 8);
+  const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&lo);
+  const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&hi);
+  uint4 packed;
+  __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const float2 p0 = __bfloat1622float2(a[2 * e]), p1 = __bfloat1622float2(a[2 * e + 1]);
+    const float2 q0 = __bfloat1622float2(b[2 * e]), q1 = __bfloat1622float2(b[2 * e + 1]);
+    o[e] = __floats2bfloat162_rn(clamped_glu(p0.x, p0.y, limit), clamped_glu(p1.x, p1.y, limit));
+    o[2 + e] = __floats2bfloat162_rn(clamped_glu(q0.x, q0.y, limit), clamped_glu(q1.x, q1.y, limit));
+  }
+  *reinterpret_cast<uint4*>(out + 8 * i) = packed;
+}
+}  // namespace ms
+
 // both [n_tokens, 2 * inter] with alternating (gate, up) columns; out [n_tokens, inter].
 MS_EXPORT int ms_clamped_glu(const void* both, int dtype, void* out, int n_tokens, int inter, float limit, cudaStream_t stream) {
   const long long total = (long long)n_tokens * inter;
   if (total <= 0) return 0;
+  if (dtype == MS_BF16 && total % 8 == 0) {
+    const long long groups = total / 8;
+    ms::launch(clamped_glu_vec_kernel, (unsigned)((groups + 255) / 256), 256, 0, stream, (const __nv_bfloat16*)both, (__nv_bfloat16*)out,
+               (size_t)groups, limit);
+    MS_CHECK_LAUNCH("clamped_glu");
+    return 0;
+  }
   const long long blocks = (total + 255) / 256;
   MS_REQUIRE(blocks < 2147483647LL, "clamped_glu: %lld elements in one launch is too many", total);
   MS_EXP_DISPATCH(dtype, (ms::launch(clamped_glu_kernel<T>, (unsigned)blocks, 256, 0, stream, (const T*)both, (T*)out, (size_t)total, limit)));

@@ -17,7 +17,7 @@
 
 namespace ms {
 
-constexpr int kConvTokens = 64;      // tokens of a request that one thread walks
+constexpr int kConvTokens = 16;      // tokens of a request that one thread walks
 constexpr int kMaxTaps = 8;
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
@@ -71,6 +71,7 @@ causal_conv_silu_kernel(const T* __restrict__ proj, int ld, int col, int channel
     }
   }
   const int t_end = min(q_len, t0 + kConvTokens);
+#pragma unroll 4
   for (int t = t0; t < t_end; ++t) {
 #pragma unroll
     for (int k = 0; k + 1 < kMaxTaps; ++k) window[k] = window[k + 1];
@@ -289,6 +290,35 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, const T* __
   }
 }
 
+// The same with one warp per (token, group) and the group's values in registers (a group of up to 32 * PER numbers): the
+// row is read once.
+template <typename T, int PER>
+__global__ void gated_group_norm_warp_kernel(const float* __restrict__ y, const T* __restrict__ proj, int ld, int z_col,
+                                             const float* __restrict__ weight, int groups, int inner, float eps,
+                                             T* __restrict__ out, long long items) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= items) return;
+  const int lane = threadIdx.x & 31;
+  const size_t token = item / groups;
+  const int size = inner / groups, c0 = (int)(item % groups) * size;
+  float v[PER];
+  float sum_sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int c = lane + 32 * i;
+    v[i] = c < size ? y[token * inner + c0 + c] * silu_f(to_float(proj[token * ld + z_col + c0 + c])) : 0.f;
+    sum_sq += v[i] * v[i];
+  }
+  const float inv = 1.0f / sqrtf(warp_sum(sum_sq) / (float)size + eps);
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int c = lane + 32 * i;
+    if (c < size) out[token * inner + c0 + c] = from_float<T>(v[i] * inv * weight[c0 + c]);
+  }
+}
+
 }  // namespace ms
 
 using namespace ms;
@@ -367,6 +397,19 @@ MS_EXPORT int ms_gated_group_norm(const float* y, const void* proj, int dtype, i
   if (n_tokens == 0 || inner == 0) return 0;
   MS_REQUIRE(groups > 0 && inner % groups == 0 && groups <= 65535, "gated_group_norm: %d channels in %d groups", inner, groups);
   const int size = inner / groups;
+  if (size <= 1024) {
+    const long long items = (long long)n_tokens * groups;
+    const long long blocks = (items + 3) / 4;
+    MS_REQUIRE(blocks < 2147483647LL, "gated_group_norm: %lld groups in one launch is too many", items);
+#define MS_GROUP_NORM(PER)                                                                                                   \
+  MS_SS_DISPATCH(dtype, (ms::launch(gated_group_norm_warp_kernel<T, PER>, (unsigned)blocks, 128, 0, stream, y, (const T*)proj, ld, \
+                                    z_col, weight, groups, inner, eps, (T*)out, items)))
+    if (size <= 128) { MS_GROUP_NORM(4); } else if (size <= 256) { MS_GROUP_NORM(8); } else if (size <= 512) { MS_GROUP_NORM(16); }
+    else { MS_GROUP_NORM(32); }
+#undef MS_GROUP_NORM
+    MS_CHECK_LAUNCH("gated_group_norm");
+    return 0;
+  }
   const int threads = size >= 1024 ? 256 : (size >= 256 ? 128 : 64);
   dim3 grid(n_tokens, groups);
   MS_SS_DISPATCH(dtype, (ms::launch(gated_group_norm_kernel<T>, grid, threads, 0, stream, y, (const T*)proj, ld, z_col, weight,
