@@ -268,6 +268,35 @@ selective_scan_kernel(const float* __restrict__ conv, int conv_ld, const T* __re
   }
 }
 
+// One block per (token, group) with the group's values in registers between the two passes (groups of up to 16 numbers per
+// thread): the row is read once.
+constexpr int kGroupNormPerThread = 16;
+
+template <typename T>
+__global__ void gated_group_norm_once_kernel(const float* __restrict__ y, const T* __restrict__ proj, int ld, int z_col,
+                                             const float* __restrict__ weight, int groups, int inner, float eps,
+                                             T* __restrict__ out) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  __shared__ float scratch[32];
+  const size_t token = blockIdx.x;
+  const int size = inner / groups, c0 = blockIdx.y * size;
+  float v[kGroupNormPerThread];
+  float sum_sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < kGroupNormPerThread; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    v[i] = c < size ? y[token * inner + c0 + c] * silu_f(to_float(proj[token * ld + z_col + c0 + c])) : 0.f;
+    sum_sq += v[i] * v[i];
+  }
+  const float inv = 1.0f / sqrtf(block_sum(sum_sq, scratch) / (float)size + eps);
+#pragma unroll
+  for (int i = 0; i < kGroupNormPerThread; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < size) out[token * inner + c0 + c] = from_float<T>(v[i] * inv * weight[c0 + c]);
+  }
+}
+
 // One block per (token, group): v = y * silu(z); out = weight * v / sqrt(mean(v^2) + eps).
 template <typename T>
 __global__ void gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ proj, int ld, int z_col,
@@ -397,21 +426,27 @@ MS_EXPORT int ms_gated_group_norm(const float* y, const void* proj, int dtype, i
   if (n_tokens == 0 || inner == 0) return 0;
   MS_REQUIRE(groups > 0 && inner % groups == 0 && groups <= 65535, "gated_group_norm: %d channels in %d groups", inner, groups);
   const int size = inner / groups;
-  if (size <= 1024) {
+  if (size <= 128) {
     const long long items = (long long)n_tokens * groups;
     const long long blocks = (items + 3) / 4;
     MS_REQUIRE(blocks < 2147483647LL, "gated_group_norm: %lld groups in one launch is too many", items);
 #define MS_GROUP_NORM(PER)                                                                                                   \
   MS_SS_DISPATCH(dtype, (ms::launch(gated_group_norm_warp_kernel<T, PER>, (unsigned)blocks, 128, 0, stream, y, (const T*)proj, ld, \
                                     z_col, weight, groups, inner, eps, (T*)out, items)))
-    if (size <= 128) { MS_GROUP_NORM(4); } else if (size <= 256) { MS_GROUP_NORM(8); } else if (size <= 512) { MS_GROUP_NORM(16); }
-    else { MS_GROUP_NORM(32); }
+    MS_GROUP_NORM(4);
 #undef MS_GROUP_NORM
     MS_CHECK_LAUNCH("gated_group_norm");
     return 0;
   }
-  const int threads = size >= 1024 ? 256 : (size >= 256 ? 128 : 64);
   dim3 grid(n_tokens, groups);
+  if (size <= 256 * kGroupNormPerThread) {
+    const int once_threads = size >= 2048 ? 256 : (size >= 512 ? 128 : 64);
+    MS_SS_DISPATCH(dtype, (ms::launch(gated_group_norm_once_kernel<T>, grid, once_threads, 0, stream, y, (const T*)proj, ld, z_col,
+                                      weight, groups, inner, eps, (T*)out)));
+    MS_CHECK_LAUNCH("gated_group_norm");
+    return 0;
+  }
+  const int threads = 256;
   MS_SS_DISPATCH(dtype, (ms::launch(gated_group_norm_kernel<T>, grid, threads, 0, stream, y, (const T*)proj, ld, z_col, weight,
                                     groups, inner, eps, (T*)out)));
   MS_CHECK_LAUNCH("gated_group_norm");
