@@ -14,6 +14,7 @@
 // A request's state vector: [taps - 1][channels] convolution inputs, oldest first, then [heads][P][N] head states
 // (zero at admission: the zeros before a sequence's start and the empty state are the same thing).
 #include "common.cuh"
+#include "elementwise_vec.cuh"
 
 namespace ms {
 
@@ -268,6 +269,46 @@ selective_scan_kernel(const float* __restrict__ conv, int conv_ld, const T* __re
   }
 }
 
+// One block per (token, group), sixteen-byte loads and stores, the group's values in registers between the two passes: each
+// thread keeps up to CHUNKS runs of eight numbers.  Group size, row lengths and z's column multiples of eight.
+template <typename T, int CHUNKS>
+__global__ void gated_group_norm_vec_kernel(const float* __restrict__ y, const T* __restrict__ proj, int ld, int z_col,
+                                            const float* __restrict__ weight, int groups, int inner, float eps,
+                                            T* __restrict__ out) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  __shared__ float scratch[32];
+  const size_t token = blockIdx.x;
+  const int size = inner / groups, c0 = blockIdx.y * size;
+  Vec8 v[CHUNKS];
+  float sum_sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < CHUNKS; ++i) {
+    const int c = (i * blockDim.x + threadIdx.x) * 8;
+    if (c < size) {
+      v[i] = load8(y + token * inner + c0 + c);
+      const Vec8 z = load8(proj + token * ld + z_col + c0 + c);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        v[i].v[e] *= silu_f(z.v[e]);
+        sum_sq += v[i].v[e] * v[i].v[e];
+      }
+    }
+  }
+  const float inv = 1.0f / sqrtf(block_sum(sum_sq, scratch) / (float)size + eps);
+#pragma unroll
+  for (int i = 0; i < CHUNKS; ++i) {
+    const int c = (i * blockDim.x + threadIdx.x) * 8;
+    if (c < size) {
+      const Vec8 w = load8(weight + c0 + c);
+      Vec8 r;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) r.v[e] = v[i].v[e] * inv * w.v[e];
+      store8(out + token * inner + c0 + c, r);
+    }
+  }
+}
+
 // One block per (token, group) with the group's values in registers between the two passes (groups of up to 16 numbers per
 // thread): the row is read once.
 constexpr int kGroupNormPerThread = 16;
@@ -426,6 +467,19 @@ MS_EXPORT int ms_gated_group_norm(const float* y, const void* proj, int dtype, i
   if (n_tokens == 0 || inner == 0) return 0;
   MS_REQUIRE(groups > 0 && inner % groups == 0 && groups <= 65535, "gated_group_norm: %d channels in %d groups", inner, groups);
   const int size = inner / groups;
+  if (size % 8 == 0 && ld % 8 == 0 && z_col % 8 == 0 && size >= 256 && size <= 8192) {
+    const int runs = size / 8;
+    const int vec_threads = runs >= 256 ? 256 : ((runs + 31) / 32) * 32;
+    const int chunks = (runs + vec_threads - 1) / vec_threads;
+    dim3 vec_grid(n_tokens, groups);
+#define MS_GROUP_NORM_VEC(C)                                                                                                  \
+  MS_SS_DISPATCH(dtype, (ms::launch(gated_group_norm_vec_kernel<T, C>, vec_grid, vec_threads, 0, stream, y, (const T*)proj, ld,     \
+                                    z_col, weight, groups, inner, eps, (T*)out)))
+    if (chunks == 1) { MS_GROUP_NORM_VEC(1); } else if (chunks == 2) { MS_GROUP_NORM_VEC(2); } else { MS_GROUP_NORM_VEC(4); }
+#undef MS_GROUP_NORM_VEC
+    MS_CHECK_LAUNCH("gated_group_norm");
+    return 0;
+  }
   if (size <= 128) {
     const long long items = (long long)n_tokens * groups;
     const long long blocks = (items + 3) / 4;
