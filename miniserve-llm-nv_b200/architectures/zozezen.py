@@ -27,12 +27,13 @@ def build_zozezen_spec(config: ZozezenConfig) -> ModelSpec:
     def stream_norm(name: str) -> PartSpec:
         return PartSpec("rms", dict(name=name, size=width, eps=eps, one_plus=True))
 
-    layers, order = [], []
+    layers, order, unused = [], [], []
     for index, layer in enumerate(config.layers):
         m = layer.mixer
         cache_of = None
         if layer.type == "attention":
-            position = PartSpec("rope", dict(head_dim=m.dim, theta=m.rot.base, rotary_dim=m.rot.dims, frequencies="float64"))
+            position = PartSpec("none") if m.rot.dims == 0 else PartSpec(
+                "rope", dict(head_dim=m.dim, theta=m.rot.base, rotary_dim=m.rot.dims, frequencies="float64"))
             mixer = PartSpec("attention", dict(
                 hidden_size=width, num_heads=m.heads, num_kv_heads=m.kv_heads, head_dim=m.dim, value_dim=m.vdim, qk_norm=True,
                 eps=eps, position=position, scale=m.scale, sink=True, output_gate=True, own_kv=m.kv_from is None,
@@ -59,10 +60,12 @@ def build_zozezen_spec(config: ZozezenConfig) -> ModelSpec:
             mixer_post_norm=stream_norm("norm1b"),
             feed_forward_post_norm=None if feed_forward is None else stream_norm("norm2b")))
         order.append(LayerRun(index, cache_of))
+        if feed_forward is None:
+            unused += [f"l{index}.norm2", f"l{index}.norm2b"]       # a checkpoint may carry them although nothing reads them
     return ModelSpec(
         vocab_size=config.vocab, hidden_size=width, embedding_name="embed", layers=tuple(layers), order=tuple(order),
         final_norm=stream_norm("final.norm"), output_name="head", max_positions=NOMINAL_MAX_POSITIONS,
-        nominal_max_positions=True)
+        nominal_max_positions=True, optional_names=tuple(unused))
 
 
 register_architecture("Zozezen", ZozezenConfig, build_zozezen_spec)

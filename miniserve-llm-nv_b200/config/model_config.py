@@ -319,9 +319,13 @@ class GatedAttentionConfig:
 
     @classmethod
     def from_dict(cls, data: Mapping[str, Any], where: str) -> "GatedAttentionConfig":
+        rot = _section(data, "rot", where)
+        if _count(rot, "dims", 0) == 0:
+            rotation = RotationConfig(base=_positive(rot, "base", where + "rot."), dims=0)      # nothing is rotated
+        else:
+            rotation = RotationConfig.from_dict(rot, where + "rot.")
         config = cls(heads=_integer(data, "heads"), kv_heads=_integer(data, "kv_heads"), dim=_integer(data, "dim"),
-                     vdim=_integer(data, "vdim"), scale=_positive(data, "scale", where),
-                     rot=RotationConfig.from_dict(_section(data, "rot", where), where + "rot."),
+                     vdim=_integer(data, "vdim"), scale=_positive(data, "scale", where), rot=rotation,
                      kv_from=None if data.get("kv_from") is None else _count(data, "kv_from", 0))
         if config.heads % config.kv_heads:
             raise ValueError(f"{where}heads {config.heads} is not a multiple of kv_heads {config.kv_heads}")

@@ -50,7 +50,10 @@ class Attention(Part):
                  output_gate: bool = False, own_kv: bool = True, gate_name: str = "g_proj.weight") -> None:
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} key/value heads")
-        if head_dim % 2 or not 2 <= head_dim <= kernels.MAX_HEAD_DIM:
+        general_form = bool(sink or output_gate or not own_kv or (value_dim is not None and value_dim != head_dim))
+        if general_form and 1 <= head_dim <= kernels.MAX_HEAD_DIM:
+            pass            # (the general form's kernels take odd head sizes too; the rotation checks its own size)
+        elif head_dim % 2 or not 2 <= head_dim <= kernels.MAX_HEAD_DIM:
             # what the general attention kernel and the fused append take; the tensor-core kernels take fewer
             # sizes, and kernels.attention_kernels() says which of them a given size gets
             raise ValueError(f"head size {head_dim} is not an even number in 2..{kernels.MAX_HEAD_DIM}")

@@ -160,3 +160,41 @@ def test_cuttings_match_plain_on_cpu(cpu_runtime, name, page_size, cutting):
             assert torch.allclose(row, expected[position], atol=2e-4, rtol=2e-4), (rid, position)
     assert not runtime.manager.requests
     assert all(a.free_count == a.num_pages for a in runtime.manager.allocators)
+
+
+def test_odd_heads_no_rotation_and_norms_that_nothing_reads(cpu_runtime, monkeypatch, tmp_path):
+    """An odd head size without any rotation, and a checkpoint that carries feed-forward norms for a layer that has no
+    feed-forward: the loader lets them be, and the engine computes what the plain implementation computes."""
+    import json
+
+    from safetensors.torch import save_file
+
+    from miniserve_b200.config import EngineConfig
+    from miniserve_b200.engine import runtime as runtime_module
+    from miniserve_b200.trace import TraceSession
+    from miniserve_b200.weights import random_tensors
+
+    config = dict(architecture="Zozezen", vocab=61, width=40, norm=dict(eps=1e-5), layers=[
+        zh.layer(zh.attn(3, 1, 7, 5, 0.3, 0), None),
+        zh.layer(zh.ssm(2, 9, 5, 2, 3, 3), zh.moe(2, 2, 2, 6, 0.9, 2, 2, 10, 1.1)),
+        zh.layer(zh.attn(2, 1, 7, 5, 0.6, 0, kv_from=0), zh.moe(3, 0, 2, 6, 0.9, 1, 1, None)),
+    ])
+    tensors = random_tensors(config, 5, "float32", 0.1)
+    zh.steer_routers(tensors, config)
+    tensors["l0.norm2"], tensors["l0.norm2b"] = torch.zeros(40), torch.zeros(40)
+    folder = tmp_path / "odd"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(config))
+    save_file({k: v.contiguous() for k, v in tensors.items()}, str(folder / "model.safetensors"))
+    runtime = runtime_module.build_runtime(folder, EngineConfig(dtype="float32", kv_block_size=4, num_kv_blocks=16, max_num_seqs=2,
+                                                               enable_prefix_cache=False, device="cpu", decode_execution="eager"))
+    tokens = helpers.random_tokens(61, 19, seed=3)
+    steps = helpers.cut_portions({"r": tokens})
+    session, outputs = TraceSession(runtime), {}
+    for record in steps:
+        outputs[record["step"]] = session.run(record).double()
+    got = helpers.collect(steps, outputs)["r"]
+    loaded_config, weights = plain.load_folder(folder)
+    expected = plain.forward(tokens, weights, loaded_config)
+    for position, row in got.items():
+        assert torch.allclose(row, expected[position], atol=2e-4, rtol=2e-4), position

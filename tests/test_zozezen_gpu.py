@@ -698,3 +698,31 @@ def test_trace_run_program_and_command_line(tmp_path, dtype):
         best = int(torch.argmax(logits))
         assert token == best or float(logits[best] - logits[token]) <= 2 * bound_of(dtype, logits)
         tokens.append(token)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("width", [40, 44])
+def test_odd_heads_no_rotation_and_norms_that_nothing_reads(tmp_path, dtype, width):
+    """An odd head size without any rotation, a width that is no multiple of eight, and a checkpoint that carries feed-forward
+    norms for a layer that has no feed-forward (the loader lets them be), in portions and in a mixed batch."""
+    from safetensors.torch import save_file
+
+    from miniserve_b200.weights import random_tensors
+
+    config = dict(architecture="Zozezen", vocab=61, width=width, norm=dict(eps=1e-5), layers=[
+        zh.layer(zh.attn(3, 1, 7, 5, 0.3, 0), None),
+        zh.layer(zh.ssm(2, 9, 5, 2, 3, 3), zh.moe(2, 2, 2, 6, 0.9, 2, 2, 10, 1.1)),
+        zh.layer(zh.attn(2, 1, 7, 5, 0.6, 0, kv_from=0), zh.moe(3, 0, 2, 6, 0.9, 1, 1, None)),
+    ])
+    tensors = random_tensors(config, 5, "bfloat16", 0.1)
+    zh.steer_routers(tensors, config)
+    tensors["l0.norm2"], tensors["l0.norm2b"] = torch.zeros(width, dtype=torch.bfloat16), torch.zeros(width, dtype=torch.bfloat16)
+    folder = tmp_path / "odd"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(config))
+    save_file({k: v.contiguous() for k, v in tensors.items()}, str(folder / "model.safetensors"))
+    requests = {f"r{i}": helpers.random_tokens(61, n, seed=30 + i) for i, n in enumerate((1, 19, 40, 9))}
+    for cutting in ("portions", "mixed"):
+        steps = CUTTINGS[cutting](requests)
+        runtime = build(folder, dtype, helpers.max_live_tokens(steps, granule=64) // 4, 4)
+        check(folder, dtype, requests, helpers.collect(steps, replay(runtime, steps)))
