@@ -129,9 +129,9 @@ def _report_attention_kernels(model: DecoderModel, dtype: torch.dtype, page_size
         if not isinstance(need, PagedKVNeed):
             continue
         n_q = getattr(mixer, "num_heads", need.num_kv_heads)
-        modified = (bool(getattr(mixer, "score_softcap", None)) or getattr(mixer, "score_bias_slopes", None) is not None
-                    or need.value_dim is not None)      # (value heads of another size: the general kernel too)
-        names = kernels.attention_kernels(dtype, need.head_dim, n_q, need.num_kv_heads, page_size, modified)
+        modified = bool(getattr(mixer, "score_softcap", None)) or getattr(mixer, "score_bias_slopes", None) is not None
+        names = kernels.attention_kernels(dtype, need.head_dim, n_q, need.num_kv_heads, page_size, modified, need.value_dim,
+                                          bool(getattr(mixer, "general", False)))
         chosen.append(dict(group=plan.group, head_dim=need.head_dim, window=need.window, **names))
         slow = dtype == torch.bfloat16 and "general" in names.values()
         log.log(logging.WARNING if slow else logging.INFO,

@@ -275,14 +275,23 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, paired: bool = False) -> 
 MAX_HEAD_DIM = 512      # of the general attention kernel (attention_generic.cu: 16 output lanes per thread)
 
 
+USE_MMA_ANY = __import__("os").environ.get("MINISERVE_B200_MMA_ANY", "1") == "1"
+
+
 def attention_kernels(dtype: torch.dtype, head_dim: int, n_q: int, n_kv: int, page_size: int,
-                      modified_scores: bool = False) -> dict:
+                      modified_scores: bool = False, value_dim: Optional[int] = None, extended: bool = False) -> dict:
     """Which kernel :func:`paged_attention` runs for these sizes: ``{"decode": name, "prompt": name}`` with the
     names ``tcgen05``, ``mma.sync`` and ``general`` (float32 arithmetic, any size; the only one of the float32
     path, and what bfloat16 falls back to for head sizes the tensor-core kernels are not built for and for
     scores with a soft cap or a distance bias)."""
     lib = library()
-    if modified_scores or dtype != torch.bfloat16 or not lib.ms_attention_mma_supports(_i(head_dim)):
+    value_dim = head_dim if value_dim is None else value_dim
+    if (USE_MMA_ANY and extended and not modified_scores and dtype == torch.bfloat16
+            and (value_dim != head_dim or not lib.ms_attention_mma_supports(_i(head_dim)))
+            and lib.ms_attention_mma_any_supports(_i(head_dim), _i(value_dim))):
+        # (``extended``: the attention has a sink, a gate or value heads of their own size)
+        return {"decode": "mma.sync (any size)", "prompt": "mma.sync (any size)"}
+    if modified_scores or value_dim != head_dim or dtype != torch.bfloat16 or not lib.ms_attention_mma_supports(_i(head_dim)):
         return {"decode": "general", "prompt": "general"}
     prompt = "mma.sync"
     if USE_TCGEN05_ATTENTION and lib.ms_attention_tcgen05_supports(_i(head_dim), _i(n_q), _i(n_kv), _i(page_size)):
@@ -347,7 +356,36 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     modified = bool(softcap) or bias_slopes is not None
     if bias_slopes is not None:
         _want(bias_slopes, "bias_slopes", torch.float32, (n_q,))
-    general = modified or value_dim != head_dim      # (the tensor-core kernels take the sink and the gate, not these)
+    # the general form (a sink, a gate, value heads of their own size) at sizes the unrolled tensor-core kernels are not built
+    # for: the tensor-core kernel whose head sizes are run-time numbers (multiples of 16 up to 128)
+    extended = sink or gate is not None or value_dim != head_dim
+    if (USE_MMA_ANY and extended and not modified and q.dtype == torch.bfloat16
+            and (value_dim != head_dim or not lib.ms_attention_mma_supports(_i(head_dim)))
+            and lib.ms_attention_mma_any_supports(_i(head_dim), _i(value_dim))):
+        def run_any(first: int, last: int, longest: int, rows: int, first_row: int = 0) -> None:
+            count = last - first
+            splits = lib.ms_attention_mma_any_splits(_i(count), _i(n_kv), _i(n_q), _i(longest), _i(max_context_len))
+            part_o = part_lse = None
+            if splits > 1:
+                part_o = torch.empty((rows * n_q * splits, value_dim), dtype=torch.float32, device=q.device)
+                part_lse = torch.empty((rows * n_q * splits,), dtype=torch.float32, device=q.device)
+            _check(lib.ms_paged_attention_mma_any(
+                _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables[first:last]), _i(block_tables.shape[1]),
+                _ptr(query_start[first:last + 1]), _ptr(context_lens[first:last]), _i(k_pool.shape[2]), _i(n_q), _i(n_kv),
+                _i(head_dim), _i(value_dim), _f(scale), _i(window if window else 0), _ptr(out), _ptr(part_o), _ptr(part_lse),
+                _i(splits), _i(count), _i(longest), _i(rows), _i(1 if sink else 0), gate_ptr, _i(gate_ld), _i(first_row), _stream()))
+
+        single = 0
+        if host_query_start and max_query_len > 1 and len(host_query_start) == n_requests + 1:
+            while single < n_requests and host_query_start[single + 1] - host_query_start[single] == 1:
+                single += 1
+        if 0 < single < n_requests:
+            run_any(0, single, 1, single)
+            run_any(single, n_requests, max_query_len, n, single)
+        else:
+            run_any(0, n_requests, max_query_len, n)
+        return
+    general = modified or value_dim != head_dim      # (the unrolled tensor-core kernels take the sink and the gate, not these)
     if general or q.dtype != torch.bfloat16 or not lib.ms_attention_mma_supports(_i(head_dim)):
         _check(lib.ms_paged_attention_generic(
             _ptr(q), _i(_code(q.dtype)), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _i(block_tables.shape[1]),

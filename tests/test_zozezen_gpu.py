@@ -202,7 +202,9 @@ def test_router_with_negative_choice_scores_and_ties():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("n_q,n_kv,d,dv,page", [(8, 1, 64, 64, 16), (4, 2, 128, 128, 8), (6, 3, 32, 32, 16), (6, 3, 24, 40, 4), (16, 4, 128, 128, 64)])
+@pytest.mark.parametrize("n_q,n_kv,d,dv,page", [(8, 1, 64, 64, 16), (4, 2, 128, 128, 8), (6, 3, 32, 32, 16), (6, 3, 24, 40, 4), (16, 4, 128, 128, 64),
+                                                 (6, 2, 48, 80, 16), (4, 2, 64, 32, 8), (8, 1, 96, 96, 16), (2, 2, 16, 128, 4), (4, 4, 112, 80, 16),
+                                                 (34, 2, 48, 48, 16)])
 @pytest.mark.parametrize("single", [False, True])
 def test_attention_kernels_with_sink_and_gate(dtype, n_q, n_kv, d, dv, page, single):
     """``paged_attention`` with the sink and the gate over unequal requests: prompt portions that continue long contexts, or
@@ -280,6 +282,7 @@ ATTENTION_ALONE = [
     (72, zh.attn(1, 1, 12, 10, 0.4, 6, 100.0)["mixer"]),
     (64, zh.attn(8, 1, 64, 64, 0.125, 64, 1000000.0)["mixer"]),
     (96, zh.attn(4, 2, 128, 32, 0.09, 64, 10000.0)["mixer"]),
+    (80, zh.attn(8, 2, 48, 80, 0.14, 32, 250000.0)["mixer"]),
 ]
 
 
@@ -569,7 +572,7 @@ LENGTHS = (1, 7, 8, 9, 16, 17, 33, 64, 65, 150, 301)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,page_size", [("a", 8), ("b", 16), ("c", 16), ("b", 4)])
+@pytest.mark.parametrize("name,page_size", [("a", 8), ("b", 16), ("c", 16), ("b", 4), ("d", 8)])
 @pytest.mark.parametrize("cutting", list(CUTTINGS))
 def test_cuttings_against_plain(tmp_path, request, dtype, name, page_size, cutting):
     """Whole prompts; last tokens decoded one by one; portions down to two tokens; unequal requests batched together in a
@@ -609,7 +612,7 @@ def test_float32_logits_do_not_depend_on_cutting_or_batch(tmp_path, name, page_s
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["a", "c"])
+@pytest.mark.parametrize("name", ["a", "c", "d"])
 def test_prefill_against_decoding_every_token(tmp_path, dtype, name):
     """The same sequence as one prompt and token by token from its first token on (a long decode over several pages, the
     state carried through every step): the two agree with the plain logits and so, within rounding, with each other."""
@@ -726,3 +729,18 @@ def test_odd_heads_no_rotation_and_norms_that_nothing_reads(tmp_path, dtype, wid
         steps = CUTTINGS[cutting](requests)
         runtime = build(folder, dtype, helpers.max_live_tokens(steps, granule=64) // 4, 4)
         check(folder, dtype, requests, helpers.collect(steps, replay(runtime, steps)))
+
+
+def test_which_attention_kernels_a_build_reports(tmp_path):
+    """bfloat16: heads of 64 and 128 with values of the same size on the unrolled tensor-core kernels; heads of 48 with values
+    of 80 (and 112 with 16) on the tensor-core kernel for any multiple of 16; sizes that are no multiples of 16 on the general
+    kernel, as everything in float32."""
+    expected = {"c": [("tcgen05", "mma.sync"), ("tcgen05", "mma.sync")],
+                "d": [("mma.sync (any size)", "mma.sync (any size)"), ("mma.sync (any size)", "mma.sync (any size)")],
+                "b": [("general", "general"), ("general", "general")]}
+    for name, kinds in expected.items():
+        folder = zh.make_folder(tmp_path, name, seed=17)
+        runtime = build(folder, "bfloat16", 16, 16)
+        assert [(k["prompt"], k["decode"]) for k in runtime.attention_kernels] == kinds, name
+        runtime = build(folder, "float32", 16, 16)
+        assert all(k["prompt"] == k["decode"] == "general" for k in runtime.attention_kernels)

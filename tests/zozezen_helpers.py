@@ -59,7 +59,15 @@ ZOZEZEN_C = dict(architecture="Zozezen", vocab=300, width=128, norm=dict(eps=1e-
     layer(attn(4, 2, 128, 128, 0.09, 64, 10000.0), moe(12, 4, 2, 32, 1.0, 4, 1, 32, 1.0)),
     layer(attn(8, 2, 128, 128, 0.09, 64, 10000.0, kv_from=3), moe(12, 4, 2, 32, 1.0, 4, 1, 32, 1.0)),
 ])
-CONFIGS = {"a": ZOZEZEN_A, "b": ZOZEZEN_B, "c": ZOZEZEN_C}
+# Head sizes that are multiples of 16 but neither equal for keys and values nor among 32 / 64 / 128: the tensor-core kernel
+# whose head sizes are run-time numbers; a layer on borrowed keys with four times the lender's query heads.
+ZOZEZEN_D = dict(architecture="Zozezen", vocab=180, width=112, norm=dict(eps=1e-5), layers=[
+    layer(attn(4, 2, 48, 80, 0.15, 32, 10000.0), moe(6, 2, 2, 16, 1.0, 2, 1, 24, 1.0)),
+    layer(ssm(4, 16, 32, 2, 4, 2), moe(5, 0, 2, 16, 1.0, 1, 1, None)),
+    layer(attn(16, 2, 48, 80, 0.2, 32, 10000.0, kv_from=0), moe(6, 2, 2, 16, 1.0, 2, 1, 24, 1.0)),
+    layer(attn(2, 2, 112, 16, 0.1, 16, 500.0), None),
+])
+CONFIGS = {"a": ZOZEZEN_A, "b": ZOZEZEN_B, "c": ZOZEZEN_C, "d": ZOZEZEN_D}
 
 POST_NORM_WEIGHT = -0.85     # the stored weight of the sublayers' output norms (1 + w = 0.15): what a sublayer adds stays small
 
