@@ -91,7 +91,8 @@ causal_conv_silu_kernel(const T* __restrict__ proj, int ld, int col, int channel
 // The recurrence.  grid (column blocks of a head, heads, requests); a block of four warps owns 4 * CP channels (columns p)
 // of one head of one request, a warp CP of them, with the 32 lanes along the state: lane j holds the entries n = j,
 // j + 32, ... (R of them) of each of its columns in registers.  The tokens' B, C and x pass through shared memory in chunks
-// of TOK tokens, two chunks deep: the asynchronous copies of the next chunk run while this one is multiplied, so the trip to
+// of `tok` tokens (at most TOK; fewer where no request of the step brings that many, so that a step of single tokens
+// holds next to no shared memory and more of its blocks are resident), two chunks deep: the asynchronous copies of the next chunk run while this one is multiplied, so the trip to
 // the second-level cache is paid once per kernel, not once per token.  Step sizes and decays (a softplus and two
 // exponentials per token and head) are computed for a chunk at a time, lane l taking token l, and handed round by shuffles.
 // y_t[p] for the warp's CP columns is reduced across the lanes in one butterfly that halves the number of values a lane
@@ -109,19 +110,21 @@ __device__ __forceinline__ void scan_copy(float* dst, const float* src, bool val
 
 // FULL: the state is a multiple of 32 numbers and the head's channels a multiple of the block's (no lane or column is idle,
 // and no bound is tested per token).
-template <typename T, int R, int CP, int TOK, bool FULL>
+// SHORT: no request of the step brings TOK tokens, and the chunks are as long as the longest portion (a run-time number).
+template <typename T, int R, int CP, int TOK, bool FULL, bool SHORT>
 __global__ void __launch_bounds__(kScanWarps * 32)
 selective_scan_kernel(const float* __restrict__ conv, int conv_ld, const T* __restrict__ proj, int ld, int dt_col,
                       const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                       float* __restrict__ states, long long state_stride, int state_offset,
                       const int* __restrict__ state_slots, const int* __restrict__ query_start, int heads, int P, int N,
-                      int groups, float* __restrict__ y, int wide) {
+                      int groups, float* __restrict__ y, int wide, int short_tok) {
   grid_dependency_wait();
   grid_dependency_launch();
   constexpr int COLS = kScanWarps * CP;
+  const int tok = SHORT ? short_tok : TOK;
   extern __shared__ __align__(16) float scan_smem[];
   const int n_pad = (N + 3) & ~3;                           // a token's B (or C) row in shared memory
-  const int stage_floats = TOK * (2 * n_pad + COLS);
+  const int stage_floats = tok * (2 * n_pad + COLS);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int head = blockIdx.y, request = blockIdx.z;
   const int block_p0 = blockIdx.x * COLS, p0 = block_p0 + warp * CP;
@@ -138,12 +141,12 @@ selective_scan_kernel(const float* __restrict__ conv, int conv_ld, const T* __re
   // one chunk's copies: rows of B and C (n_pad floats each, in pieces of four floats or single floats) and COLS values of x
   auto fetch = [&](int chunk, int stage) {
     float* b_s = scan_smem + stage * stage_floats;
-    float* c_s = b_s + TOK * n_pad;
-    float* x_s = c_s + TOK * n_pad;
-    const int t0 = chunk * TOK;
+    float* c_s = b_s + tok * n_pad;
+    float* x_s = c_s + tok * n_pad;
+    const int t0 = chunk * tok;
     if (wide) {
       const int pieces = n_pad / 4;
-      for (int i = tid; i < TOK * pieces; i += kScanWarps * 32) {
+      for (int i = tid; i < tok * pieces; i += kScanWarps * 32) {
         const int t = i / pieces, piece = (i % pieces) * 4;
         const bool valid = t0 + t < q_len;
         const size_t row = valid ? (size_t)(t0 + t) * conv_ld : 0;
@@ -151,7 +154,7 @@ selective_scan_kernel(const float* __restrict__ conv, int conv_ld, const T* __re
         scan_copy(c_s + t * n_pad + piece, conv_c + row + piece, valid, true);
       }
     } else {
-      for (int i = tid; i < TOK * N; i += kScanWarps * 32) {
+      for (int i = tid; i < tok * N; i += kScanWarps * 32) {
         const int t = i / N, n = i % N;
         const bool valid = t0 + t < q_len;
         const size_t row = valid ? (size_t)(t0 + t) * conv_ld : 0;
@@ -159,7 +162,7 @@ selective_scan_kernel(const float* __restrict__ conv, int conv_ld, const T* __re
         scan_copy(c_s + t * n_pad + n, conv_c + row + n, valid, false);
       }
     }
-    for (int i = tid; i < TOK * COLS; i += kScanWarps * 32) {
+    for (int i = tid; i < tok * COLS; i += kScanWarps * 32) {
       const int t = i / COLS, col = i % COLS;
       const bool valid = t0 + t < q_len && block_p0 + col < P;
       scan_copy(x_s + i, conv_x + (valid ? (size_t)(t0 + t) * conv_ld + col : 0), valid, false);
@@ -167,7 +170,7 @@ selective_scan_kernel(const float* __restrict__ conv, int conv_ld, const T* __re
     asm volatile("cp.async.commit_group;\n" ::);
   };
 
-  const int chunks = (q_len + TOK - 1) / TOK;
+  const int chunks = (q_len + tok - 1) / tok;
   fetch(0, 0);
   float s[CP][R];
 #pragma unroll
@@ -179,9 +182,9 @@ selective_scan_kernel(const float* __restrict__ conv, int conv_ld, const T* __re
     }
   const float a = -expf(a_log[head]);
   const float bias = dt_bias[head], skip = d_skip[head];
-  auto raw_step = [&](int chunk) {                          // the step-size logit of token chunk * TOK + lane
-    const int t = chunk * TOK + lane;
-    return (lane < TOK && t < q_len) ? to_float(proj[(size_t)(q0 + t) * ld + dt_col + head]) : 0.f;
+  auto raw_step = [&](int chunk) {                          // the step-size logit of token chunk * tok + lane
+    const int t = chunk * tok + lane;
+    return (lane < tok && t < q_len) ? to_float(proj[(size_t)(q0 + t) * ld + dt_col + head]) : 0.f;
   };
   float raw_next = raw_step(0);
   for (int chunk = 0; chunk < chunks; ++chunk) {
@@ -197,9 +200,9 @@ selective_scan_kernel(const float* __restrict__ conv, int conv_ld, const T* __re
     const float my_step = raw > 20.f ? raw : log1pf(expf(raw));         // softplus; above 20 the two agree in float32
     const float my_decay = expf(a * my_step);
     const float* b_s = scan_smem + (chunk & 1) * stage_floats;
-    const float* c_s = b_s + TOK * n_pad;
-    const float* x_s = c_s + TOK * n_pad + warp * CP;
-    const int t0 = chunk * TOK, count = min(TOK, q_len - t0);
+    const float* c_s = b_s + tok * n_pad;
+    const float* x_s = c_s + tok * n_pad + warp * CP;
+    const int t0 = chunk * tok, count = min(tok, q_len - t0);
     if (p0 < P) {
       float* y_at = y_row + (size_t)t0 * inner;
 #pragma unroll 4
@@ -422,12 +425,13 @@ MS_EXPORT int ms_scan_max_state() { return kScanMaxState; }
 
 // conv float32 [tokens, conv_ld] = [x: heads * P | B: groups * N | C: groups * N]; dt is column dt_col + head of proj;
 // dt_bias, a_log, d float32 [heads]; the heads' states [heads][P][N] at state_offset of a slot's row; y float32
-// [tokens, heads * P].
+// [tokens, heads * P].  max_query_len: an upper bound of the tokens a request brings (it sizes the chunks).
 MS_EXPORT int ms_selective_scan(const float* conv, int conv_ld, const void* proj, int dtype, int ld, int dt_col,
                                 const float* dt_bias, const float* a_log, const float* d, float* states,
                                 long long state_stride, int state_offset, const int* state_slots, const int* query_start,
-                                int n_requests, int heads, int p, int n_state, int groups, float* y, cudaStream_t stream) {
-  if (n_requests == 0) return 0;
+                                int n_requests, int max_query_len, int heads, int p, int n_state, int groups, float* y,
+                                cudaStream_t stream) {
+  if (n_requests == 0 || max_query_len <= 0) return 0;
   MS_REQUIRE(heads > 0 && groups > 0 && heads % groups == 0, "selective_scan: %d heads in %d groups", heads, groups);
   MS_REQUIRE(n_state >= 1 && n_state <= kScanMaxState, "selective_scan: a state of %d numbers per channel outside 1..%d",
              n_state, kScanMaxState);
@@ -441,17 +445,20 @@ MS_EXPORT int ms_selective_scan(const float* conv, int conv_ld, const void* proj
 #define MS_SCAN(R, CP, TOK)                                                                                                    \
   {                                                                                                                            \
     dim3 grid((p + kScanWarps * CP - 1) / (kScanWarps * CP), heads, n_requests);                                              \
-    const size_t smem = (size_t)2 * TOK * (2 * ((n_state + 3) & ~3) + kScanWarps * CP) * sizeof(float);                        \
+    const int tok = max_query_len < TOK ? max_query_len : TOK;                                                                \
+    const size_t smem = (size_t)2 * tok * (2 * ((n_state + 3) & ~3) + kScanWarps * CP) * sizeof(float);                        \
     MS_SS_DISPATCH(dtype, {                                                                                                    \
-      auto kernel = full ? selective_scan_kernel<T, R, CP, TOK, true> : selective_scan_kernel<T, R, CP, TOK, false>;           \
-      static bool configured[2] = {false, false};                                                                                          \
-      if (!configured[full]) {                                                                                                 \
+      const bool brief = tok < TOK;                                                                                            \
+      auto kernel = brief ? (full ? selective_scan_kernel<T, R, CP, TOK, true, true> : selective_scan_kernel<T, R, CP, TOK, false, true>)  \
+                          : (full ? selective_scan_kernel<T, R, CP, TOK, true, false> : selective_scan_kernel<T, R, CP, TOK, false, false>); \
+      static bool configured[4] = {false, false, false, false};                                                                                          \
+      if (!configured[full + 2 * brief]) {                                                                                     \
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * TOK * (2 * 32 * R + kScanWarps * CP) * 4); \
         if (e != cudaSuccess) MS_FAIL("selective_scan: shared memory refused: %s", cudaGetErrorString(e));                     \
-        configured[full] = true;                                                                                               \
+        configured[full + 2 * brief] = true;                                                                                   \
       }                                                                                                                        \
       ms::launch(kernel, grid, kScanWarps * 32, smem, stream, conv, conv_ld, (const T*)proj, ld, dt_col, dt_bias, a_log, d,    \
-                 states, state_stride, state_offset, state_slots, query_start, heads, p, n_state, groups, y, wide);            \
+                 states, state_stride, state_offset, state_slots, query_start, heads, p, n_state, groups, y, wide, tok);       \
     })                                                                                                                         \
   }
   if (per_lane <= 1) MS_SCAN(1, 4, 32) else if (per_lane <= 2) MS_SCAN(2, 4, 32) else if (per_lane <= 4) MS_SCAN(4, 4, 32) else MS_SCAN(8, 2, 16)

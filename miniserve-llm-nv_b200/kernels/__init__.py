@@ -661,12 +661,14 @@ def causal_conv_silu(proj: torch.Tensor, col: int, weight: torch.Tensor, bias: t
 
 def selective_scan(conv: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
                    d: torch.Tensor, states: torch.Tensor, state_offset: int, state_slots: torch.Tensor,
-                   query_start: torch.Tensor, heads: int, head_dim: int, state: int, groups: int, y: torch.Tensor) -> None:
+                   query_start: torch.Tensor, heads: int, head_dim: int, state: int, groups: int, y: torch.Tensor,
+                   max_query_len: Optional[int] = None) -> None:
     """The selective recurrence over each request's tokens, from and into the request's state.  ``conv`` float32
     ``[N, heads * head_dim + 2 * groups * state]`` = ``[x | B | C]``; the step size of head h is ``softplus(proj[t,
     dt_col + h] + dt_bias[h])``; per head (group ``h // (heads / groups)``) ``S = exp(-exp(a_log) dt) S + dt B x^T`` and
     ``y = S^T C + d x``.  ``states[slot, state_offset:]`` holds float32 ``[heads, head_dim, state]``.  ``y`` float32
-    ``[N, heads * head_dim]``."""
+    ``[N, heads * head_dim]``.  ``max_query_len``: an upper bound of the tokens a request brings (None: the batch's size); the
+    kernel sizes its chunks by it, so a step of single tokens should say 1."""
     n, ld = proj.shape
     inner = heads * head_dim
     _want(proj, "proj")
@@ -682,8 +684,8 @@ def selective_scan(conv: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias:
     stride = _state_rows(states, state_offset, inner * state)
     _check(library().ms_selective_scan(_ptr(conv), _i(conv.shape[1]), _ptr(proj), _i(_code(proj.dtype)), _i(ld), _i(dt_col),
                                        _ptr(dt_bias), _ptr(a_log), _ptr(d), _ptr(states), stride, _i(state_offset),
-                                       _ptr(state_slots), _ptr(query_start), _i(n_requests), _i(heads), _i(head_dim), _i(state),
-                                       _i(groups), _ptr(y), _stream()))
+                                       _ptr(state_slots), _ptr(query_start), _i(n_requests), _i(n if max_query_len is None else max_query_len),
+                                       _i(heads), _i(head_dim), _i(state), _i(groups), _ptr(y), _stream()))
 
 
 def gated_group_norm(y: torch.Tensor, proj: torch.Tensor, z_col: int, weight: torch.Tensor, groups: int, eps: float,

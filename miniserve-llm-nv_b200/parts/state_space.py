@@ -99,7 +99,8 @@ class StateSpace(Part):
                                  ctx.query_start, ctx.max_query_len, conv)
         y = ctx.buffer("state_space.y", (n, self.inner), torch.float32)
         kernels.selective_scan(conv, proj, self.dt_col, self.dt_bias, self.a_log, self.d, cache.states, self.conv_state,
-                               ctx.state_slots, ctx.query_start, self.heads, self.head_dim, self.state, self.groups, y)
+                               ctx.state_slots, ctx.query_start, self.heads, self.head_dim, self.state, self.groups, y,
+                               max_query_len=ctx.max_query_len)
         gated = ctx.buffer("state_space.gated", (n, self.inner), x.dtype)
         kernels.gated_group_norm(y, proj, self.z_col, self.norm_weight, self.norm_groups, self.eps, gated)
         out = ctx.buffer("state_space.out", (n, self.hidden_size), x.dtype)

@@ -394,7 +394,7 @@ def causal_conv_silu(proj, col, weight, bias, states, state_offset, state_slots,
 
 
 def selective_scan(conv, proj, dt_col, dt_bias, a_log, d, states, state_offset, state_slots, query_start, heads, head_dim,
-                   state, groups, y):
+                   state, groups, y, max_query_len=None):
     inner = heads * head_dim
     for r in range(state_slots.numel()):
         lo, hi = int(query_start[r]), int(query_start[r + 1])
