@@ -347,8 +347,11 @@ expert_linear_kernel(const T* __restrict__ A, int lda, const int* __restrict__ o
 // steps of 32 in three stages, which fit three blocks on a multiprocessor instead of two: steps of few rows, which only
 // stream the experts' weights, 25 -> 19 us per launch, half the barriers and twice the bytes on their way; prompt steps
 // 155 -> 147 us.)
-constexpr int GBM = 64, GBN = 128, GBK = 64, GSTAGES = 4;
+// Where the segments are long (prompt steps) the tiles have 128 rows, so that every weight fragment a warp fetches from shared
+// memory feeds four products instead of two (three stages then, two blocks a multiprocessor as before).
+constexpr int GBN = 128, GBK = 64;
 
+template <int GBM, int GSTAGES>
 __global__ void __launch_bounds__(256)
 expert_linear_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int* __restrict__ order, int top,
                          const __nv_bfloat16* __restrict__ W, __nv_bfloat16* __restrict__ C, int ldc,
@@ -401,9 +404,10 @@ expert_linear_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int
     cp_async_commit();
   }
   const int warp_m = warp >> 2, warp_n = warp & 3;
-  float acc[2][4][4];
+  constexpr int MI = GBM / 32;          // 16-row pieces of a warp's rows
+  float acc[MI][4][4];
 #pragma unroll
-  for (int i = 0; i < 2; ++i)
+  for (int i = 0; i < MI; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
   for (int kt = 0; kt < k_tiles; ++kt) {
@@ -415,15 +419,15 @@ expert_linear_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int
     const int stage = kt % GSTAGES;
 #pragma unroll
     for (int kk = 0; kk < GBK / 16; ++kk) {
-      unsigned a[2][4], b[2][4];
+      unsigned a[MI][4], b[2][4];
 #pragma unroll
-      for (int mi = 0; mi < 2; ++mi)
-        ldmatrix_x4(a[mi], &As[stage][warp_m * 32 + mi * 16 + (lane & 15)][kk * 16 + (lane >> 4) * 8]);
+      for (int mi = 0; mi < MI; ++mi)
+        ldmatrix_x4(a[mi], &As[stage][warp_m * (GBM / 2) + mi * 16 + (lane & 15)][kk * 16 + (lane >> 4) * 8]);
 #pragma unroll
       for (int np = 0; np < 2; ++np)
         ldmatrix_x4(b[np], &Bs[stage][warp_n * 32 + np * 16 + (lane & 7) + (lane >> 4) * 8][kk * 16 + ((lane >> 3) & 1) * 8]);
 #pragma unroll
-      for (int mi = 0; mi < 2; ++mi)
+      for (int mi = 0; mi < MI; ++mi)
 #pragma unroll
         for (int np = 0; np < 2; ++np) {
           mma_bf16(acc[mi][2 * np], a[mi], b[np][0], b[np][1]);
@@ -433,14 +437,14 @@ expert_linear_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int
   }
   cp_async_wait<0>();
 #pragma unroll
-  for (int mi = 0; mi < 2; ++mi)
+  for (int mi = 0; mi < MI; ++mi)
 #pragma unroll
     for (int ni = 0; ni < 4; ++ni) {
       const int n = n0 + warp_n * 32 + ni * 8 + (lane & 3) * 2;
       if (n >= N) continue;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const int m = m0 + warp_m * 32 + mi * 16 + (lane >> 2) + half * 8;
+        const int m = m0 + warp_m * (GBM / 2) + mi * 16 + (lane >> 2) + half * 8;
         if (m >= end) continue;
         float v0 = acc[mi][ni][2 * half], v1 = acc[mi][ni][2 * half + 1];
         if (activation == kActClampedGlu) {         // (v0, v1) are a feature's gate and up sums
@@ -597,16 +601,19 @@ MS_EXPORT int ms_expert_linear(const void* A, int dtype, int lda, const int* ord
   const int row_tiles = (pairs + EBM - 1) / EBM + experts;      // every segment may end in a partial tile
   MS_REQUIRE(row_tiles <= 65535, "expert_linear: %d rows in one launch is too many", pairs);
   if (dtype == MS_BF16 && K % 8 == 0 && N % 8 == 0 && lda % 8 == 0 && (ldc % 2 == 0 || activation == kActClampedGlu)) {
-    static_assert(GBM == EBM, "the two kernels walk the same row tiles");
-    dim3 mma_grid((N + GBN - 1) / GBN, row_tiles);
-    constexpr size_t smem = sizeof(__nv_bfloat16) * GSTAGES * (GBM + GBN) * (GBK + 8);
-    static bool allowed = false;
-    if (!allowed) {
-      cudaError_t e = cudaFuncSetAttribute(expert_linear_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    // long segments (256 rows an expert on average, or more): tiles of 128 rows; else tiles of 64
+    const bool tall = pairs >= 256 * experts;
+    const int rows = tall ? 128 : 64, stages = tall ? 3 : 4;
+    dim3 mma_grid((N + GBN - 1) / GBN, (pairs + rows - 1) / rows + experts);
+    const size_t smem = sizeof(__nv_bfloat16) * stages * (rows + GBN) * (GBK + 8);
+    auto kernel = tall ? expert_linear_mma_kernel<128, 3> : expert_linear_mma_kernel<64, 4>;
+    static bool allowed[2] = {false, false};
+    if (!allowed[tall]) {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) MS_FAIL("expert_linear: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
-      allowed = true;
+      allowed[tall] = true;
     }
-    ms::launch(expert_linear_mma_kernel, mma_grid, 256, smem, stream, (const __nv_bfloat16*)A, lda, order, top,
+    ms::launch(kernel, mma_grid, 256, smem, stream, (const __nv_bfloat16*)A, lda, order, top,
                (const __nv_bfloat16*)W, (__nv_bfloat16*)C, ldc, offsets, experts, N, K, activation, limit);
     MS_CHECK_LAUNCH("expert_linear (tensor cores)");
     return 0;
